@@ -1,0 +1,128 @@
+/* mxb200: a B200-native (sm_100a) MXFP8 Linear engine behind a C ABI.
+ *
+ * Drop-in for the torch-free kernel seam of nanochat-cpp's --fp8-recipe=mxfp8 / --gemm backend
+ * (namespace nanochat::kernels). Every entry point takes plain device pointers, sizes and a CUDA stream
+ * (passed as void*, a cudaStream_t), launches asynchronously on that stream against the current device and
+ * returns an mxb200_status. Nothing here allocates device memory unless its comment says so; outputs,
+ * scale buffers and the optional split-K workspace belong to the caller. There is no CPU fallback: on a
+ * machine without an sm_100 GPU the calls fail with MXB200_ERR_DEVICE.
+ *
+ * Layout contract (src/nanochat/model/fp8/fp8_kernel.h:24-39, mx_kernel.cuh:29-44 in nanochat-cpp):
+ *  - data: E4M3 bytes, row-major; one E8M0 scale byte per 32 consecutive values of a row, the smallest power
+ *    of two with max|block| * 2^-e <= 448 (or the floor rule, see mxb200_scale_rule).
+ *  - scales: cuBLAS's swizzled layout, 128 rows x 4 blocks per 512-byte tile, tiles row-major; the byte of
+ *    (row r, block b) is ((r >> 7) * tiles + (b >> 2)) * 512 + (r & 31) * 16 + ((r >> 5) & 3) * 4 + (b & 3).
+ */
+#ifndef MXB200_H_
+#define MXB200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define MXB200_API __attribute__((visibility("default")))
+#else
+#define MXB200_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum mxb200_status {
+  MXB200_OK = 0,
+  MXB200_ERR_SHAPE = 1,      /* a dimension is not a multiple the kernel needs, or is not positive */
+  MXB200_ERR_ALIGNMENT = 2,  /* a pointer or leading dimension is not 16-byte aligned */
+  MXB200_ERR_NULL = 3,       /* a required pointer is null */
+  MXB200_ERR_ARGUMENT = 4,   /* an enum or flag is out of range, or a combination is unsupported */
+  MXB200_ERR_WORKSPACE = 5,  /* the workspace is missing or smaller than mxb200_gemm_workspace_bytes says */
+  MXB200_ERR_DEVICE = 6,     /* no CUDA device, or the current device is not sm_100 */
+  MXB200_ERR_DRIVER = 7,     /* the driver refused a tensor-map encode */
+  MXB200_ERR_LAUNCH = 8,     /* the kernel launch itself failed (cudaGetLastError) */
+  MXB200_ERR_WATCHDOG = 9    /* a bounded device-side wait ran out; see mxb200_device_status */
+} mxb200_status;
+
+/* Which power of two scales a block. REFERENCE is nanochat-cpp's rule, 2^ceil(log2(amax / 448)), which never
+ * needs saturation (mx_kernel.cuh:29-34). OCP_FLOOR is 2^(floor(log2(amax)) - 8); values in (448, 512) times
+ * the scale then saturate to +-448. */
+typedef enum mxb200_scale_rule { MXB200_SCALE_REFERENCE = 0, MXB200_SCALE_OCP_FLOOR = 1 } mxb200_scale_rule;
+
+/* Value transform applied while loading, before the block maximum (fp8_kernel.cu:44-50). */
+typedef enum mxb200_prologue { MXB200_PROLOGUE_NONE = 0, MXB200_PROLOGUE_RELU_SQUARE = 1 } mxb200_prologue;
+
+/* Where one layout of a quantized tensor goes. ABI-identical to nanochat::kernels::MxOut
+ * (src/nanochat/model/fp8/fp8_kernel.h:28-33), so a sub-block of a larger buffer (merged q/k/v) is a view:
+ * data + row0 * ld + col0, scale + ((row0 / 128) * scale_tiles + col0 / 128) * 512 (fp8.cpp:117-120). */
+typedef struct mxb200_mx_out {
+  void* data;          /* e4m3; null: this layout is not written */
+  int64_t ld;          /* row stride of data, bytes */
+  void* scale;         /* e8m0, at this view's first tile */
+  int64_t scale_tiles; /* tiles per 128 rows in the whole scale buffer (its blocks per row / 4) */
+} mxb200_mx_out;
+
+/* Replaces nanochat::kernels::quantize_mx (src/nanochat/model/fp8/fp8_kernel.h:35-39; kernels
+ * nanochat_mx_quantize_{bf16,f32,relu_square_bf16}, fp8_kernel.cu:197-205).
+ * x: (rows, cols) contiguous bf16 (x_bf16 != 0) or fp32. out: x scaled along its rows; out_t: x's transpose
+ * (cols, rows) scaled along its own rows. rows, cols % 128 == 0 (the callers' mx_fits, fp8.h:86-88);
+ * x, data pointers and lds 16-byte aligned. prologue RELU_SQUARE quantizes bf16(relu(x)^2), bf16 x only. */
+MXB200_API int mxb200_quantize_mx(const void* x, int x_bf16, int64_t rows, int64_t cols, mxb200_mx_out out, mxb200_mx_out out_t,
+                       int prologue, int scale_rule, void* stream);
+
+/* Replaces nanochat::kernels::quantize_mx_relu_square_bwd (fp8_kernel.h:41-43, fp8_kernel.cu:207-210):
+ * quantizes dh = bf16(h > 0 ? g * 2h : 0) from bf16 g, h (rows, cols) without writing dh. */
+MXB200_API int mxb200_quantize_mx_relu_square_bwd(const void* g, const void* h, int64_t rows, int64_t cols, mxb200_mx_out out,
+                                       mxb200_mx_out out_t, int scale_rule, void* stream);
+
+/* Replaces nanochat::kernels::cutlass_mx_gemm_bf16 (src/nanochat/model/fp8/mx_gemm_kernel.h:13-17).
+ * d (M, N) bf16 row-major = a (M, K) . b (N, K)^T; a, b row-major e4m3 with their swizzled e8m0 scales along K;
+ * fp32 accumulation, one round-to-nearest-even to bf16. M, N, K % 128 == 0, pointers 16-byte aligned.
+ * resid (optional, (M, N) bf16): the fused residual add, d = bf16(float(bf16(acc)) + float(resid)), the two
+ * roundings of the reference's separate add (src/nanochat/model/ops/residual_norm_kernel.cu:96-104).
+ * resid may alias d. Needs no workspace. */
+MXB200_API int mxb200_gemm_bf16(const void* a, const void* a_scale, const void* b, const void* b_scale, void* d, const void* resid,
+                     int64_t M, int64_t N, int64_t K, void* stream);
+
+/* Replaces nanochat::kernels::cutlass_mx_gemm_f32 (mx_gemm_kernel.h:19-22): fp32 d (+)= alpha * a . b^T.
+ * alpha: a device fp32 scalar or null (= 1); accumulate != 0: d += (beta 1), else d =. Needs no workspace
+ * (one CTA owns each output tile for the whole of K). */
+MXB200_API int mxb200_gemm_f32(const void* a, const void* a_scale, const void* b, const void* b_scale, float* d, int64_t M,
+                    int64_t N, int64_t K, const float* alpha, int accumulate, void* stream);
+
+/* Output kinds of the split-K entry point. */
+typedef enum mxb200_out_kind { MXB200_OUT_BF16 = 0, MXB200_OUT_F32 = 1 } mxb200_out_kind;
+
+/* Deterministic split-K for long-K, few-tile shapes (the weight gradients: K = tokens). The K range is cut
+ * into `splits` slices run by different CTAs; partial tiles go through `workspace` and are summed in slice
+ * order by whichever CTA finishes last, so results do not depend on timing. Counterpart of the reference's
+ * split-K choice for these shapes (src/nanochat/model/fp8/mx_gemm.cpp:269-274, 293-314).
+ * mxb200_gemm_splits picks a slice count for a shape on the current device (1 = not worth splitting);
+ * mxb200_gemm_workspace_bytes gives the bytes `workspace` must hold for that count (0 when splits == 1).
+ * The workspace needs no initialisation and may be reused by later calls on the same stream. */
+MXB200_API int mxb200_gemm_splits(int64_t M, int64_t N, int64_t K);
+MXB200_API size_t mxb200_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int splits);
+/* out_kind BF16: d is bf16, resid optional, alpha/accumulate ignored. F32: d is fp32, resid must be null. */
+MXB200_API int mxb200_gemm_splitk(const void* a, const void* a_scale, const void* b, const void* b_scale, void* d, int out_kind,
+                       const void* resid, int64_t M, int64_t N, int64_t K, const float* alpha, int accumulate,
+                       int splits, void* workspace, size_t workspace_bytes, void* stream);
+
+/* Static message for a status (the reference's seam returns const char* messages, mx_gemm_kernel.h:12). */
+MXB200_API const char* mxb200_strerror(int status);
+
+/* Every device-side wait in the GEMM is bounded; a wait that runs out records where in a device word and the
+ * kernel returns instead of spinning. This reads that word for the current device (0 = none) and clears it.
+ * Synchronises the device. */
+MXB200_API int mxb200_device_status(uint32_t* word);
+
+/* Tuning knobs for measurement, process-wide: tile width (128 or 256; 0 = choose per shape) and the number of
+ * CTAs of the persistent grid (0 = one per SM). Not part of the reference interface. */
+MXB200_API int mxb200_set_gemm_config(int tile_n, int max_ctas);
+
+/* How many kernels this library has launched in this process (for benchmark accounting). */
+MXB200_API uint64_t mxb200_launch_count(void);
+
+MXB200_API int mxb200_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MXB200_H_ */

@@ -1,0 +1,696 @@
+// Block-scaled MXFP8 GEMM for sm_100a: D[M,N] = A[M,K] . B[N,K]^T, E4M3 operands with one E8M0 scale per 32
+// values along K (cuBLAS-swizzled scale tiles), fp32 accumulation in tensor memory.
+// Replaces nanochat-cpp's CUTLASS Sm120 kernels (src/nanochat/model/fp8/mx_gemm_kernel.cu:341-351) behind the
+// same contract (mx_gemm_kernel.h:13-22); forward, dgrad and wgrad all use this one K-major x K-major layout.
+//
+// Structure (one CTA per SM, persistent over output tiles, 192 threads):
+//   warp 0      producer: TMA loads of a 128 x 128-byte A tile and a BN x 128-byte B tile (128-byte swizzle)
+//               plus untiled bulk copies of the 512-byte scale tiles, into a ring of shared-memory stages
+//               guarded by full/empty mbarriers. No cluster multicast anywhere.
+//   warp 1      MMA issuer (one thread): per stage, tcgen05.cp moves the scale tiles into TMEM (4 columns per
+//               128 rows, byte = K block), then four tcgen05.mma kind::mxf8f6f4.block_scale steps of K = 32;
+//               tcgen05.commit releases the stage and, after the last K step, publishes the accumulator.
+//   warps 2-5   epilogue: tcgen05.ld of the fp32 accumulator (each warp its own 32-lane quarter), then bf16
+//               (optional residual add with the reference's two roundings) or fp32 (=, +=, device alpha)
+//               stores of 32 bytes per thread.
+// Two accumulator buffers let the epilogue of tile i overlap the main loop of tile i+1. With BN = 256 they
+// overlap by 32 TMEM columns ([0,256) and [224,480), scales at [480,492)); the epilogue drains the shared
+// columns first and signals that separately, so the next main loop starts after one 32-column read.
+// Split-K (weight gradients, K = tokens): partial tiles go to a caller-provided workspace and the CTA that
+// finishes a tile last sums the slices in fixed order, so results are deterministic.
+// Every wait is bounded: after kWaitLimitNs a wait records its site in a device word, raises a CTA-wide abort
+// flag that all other waits poll, and the kernel drains and returns.
+#include <algorithm>
+#include <mutex>
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include "internal.h"
+#include "mx_common.cuh"
+#include "ptx_sm100.cuh"
+
+namespace mxb200 {
+
+// one watchdog word per device context (module-scope device variable: no allocation)
+__device__ uint32_t g_watchdog_word;
+
+namespace {
+
+constexpr int kBM = 128;
+constexpr int kBK = 128;  // bytes == elements; one 128-byte swizzle atom wide
+constexpr int kThreads = 192;
+constexpr int kEpilogueThreads = 128;
+constexpr uint32_t kTmemCols = 512;
+constexpr uint64_t kWaitLimitNs = 2000000000ull;
+
+enum OutKind : int { kOutBf16 = 0, kOutF32 = 1 };
+
+// where a wait gave up (stored in the watchdog word's low byte)
+enum WaitSite : uint32_t {
+  kSiteProducerEmpty = 1,
+  kSiteMmaFull = 2,
+  kSiteMmaTmemEmpty = 3,
+  kSiteMmaOverlap = 4,
+  kSiteEpilogueFull = 5,
+  kSiteEpilogueSync = 6,
+};
+
+template <int BN>
+struct Config {
+  static constexpr int kStages = BN == 256 ? 4 : 6;
+  static constexpr int kSfbTiles = BN / 128;
+  static constexpr uint32_t kABytes = kBM * kBK;
+  static constexpr uint32_t kBBytes = BN * kBK;
+  static constexpr uint32_t kSfBytes = kScaleTileBytes * (1 + kSfbTiles);
+  // TMEM columns: two accumulator buffers, then scales of A (4 columns) and B (4 per 128 rows)
+  static constexpr bool kOverlap = BN == 256;
+  static constexpr uint32_t kAcc0 = 0;
+  static constexpr uint32_t kAcc1 = kOverlap ? 224 : BN;
+  static constexpr uint32_t kSfaCol = kOverlap ? 480 : 2 * BN;
+  static constexpr uint32_t kSfbCol = kSfaCol + 4;
+  static constexpr size_t kSmemBytes =
+        1024 /* alignment slack */ + static_cast<size_t>(kStages) * (kABytes + kBBytes + kSfBytes) + 256 /* barriers */;
+};
+
+struct GemmParams {
+  const uint8_t* a_scale;
+  const uint8_t* b_scale;
+  void* d;
+  const void* resid;
+  const float* alpha;
+  float* partials;     // split-K: [tile][split][128 * BN] fp32
+  uint32_t* counters;  // split-K: [tile], zero on entry, zero on exit
+  int M, N, K;
+  int tiles_m, tiles_n;
+  int k_tiles_total;   // K / 128
+  int k_tiles_split;   // K tiles per split
+  int splits;
+  int panel;           // n-tiles per raster panel
+  int out_kind;
+  int accumulate;
+  bool wide;  // d and resid are 32-byte aligned: 256-bit global accesses
+};
+
+struct Barriers {
+  uint64_t full[8];
+  uint64_t empty[8];
+  uint64_t tmem_full[2];
+  uint64_t tmem_empty[2];
+  uint64_t overlap_free;
+  uint64_t epi_sync;
+  uint32_t tmem_base;
+  uint32_t abort_flag;
+  uint32_t last_flag;
+};
+
+__device__ __forceinline__ bool wait_bounded(uint64_t* bar, uint32_t parity, Barriers* bars, uint32_t site) {
+  if (mbar_try_wait(bar, parity))
+    return true;
+  const uint64_t t0 = global_timer_ns();
+  uint32_t spins = 0;
+  while (!mbar_try_wait(bar, parity)) {
+    if ((++spins & 63u) == 0) {
+      if (*reinterpret_cast<volatile uint32_t*>(&bars->abort_flag) != 0)
+        return false;
+      if (global_timer_ns() - t0 > kWaitLimitNs) {
+        *reinterpret_cast<volatile uint32_t*>(&bars->abort_flag) = 1;
+        atomicCAS(&g_watchdog_word, 0u, 0x80000000u | (blockIdx.x << 8) | site);
+        return false;
+      }
+    }
+  }
+  return true;
+}
+
+struct TileCoord {
+  int m, n, split, tile;
+};
+
+__device__ __forceinline__ TileCoord decode_unit(const GemmParams& p, int unit) {
+  TileCoord c;
+  c.tile = unit / p.splits;
+  c.split = unit - c.tile * p.splits;
+  const int panel_tiles = p.panel * p.tiles_m;
+  const int pi = c.tile / panel_tiles, rem = c.tile - pi * panel_tiles;
+  const int width = min(p.panel, p.tiles_n - pi * p.panel);
+  c.m = rem / width;
+  c.n = pi * p.panel + (rem - c.m * width);
+  return c;
+}
+
+// 32 bytes to / from global memory: one 256-bit access when the address allows, else two 128-bit ones
+// (the interface only promises 16-byte alignment).
+__device__ __forceinline__ void store_u32x8(void* p, const uint32_t* w, bool wide) {
+  if (wide) {
+    asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "r"(w[0]), "r"(w[1]), "r"(w[2]),
+                 "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7])
+                 : "memory");
+  } else {
+    reinterpret_cast<uint4*>(p)[0] = make_uint4(w[0], w[1], w[2], w[3]);
+    reinterpret_cast<uint4*>(p)[1] = make_uint4(w[4], w[5], w[6], w[7]);
+  }
+}
+
+__device__ __forceinline__ void load_u32x8(const void* p, uint32_t* w, bool wide) {
+  if (wide) {
+    asm volatile("ld.global.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]), "=r"(w[4]), "=r"(w[5]), "=r"(w[6]), "=r"(w[7])
+                 : "l"(p)
+                 : "memory");
+  } else {
+    const uint4 a = reinterpret_cast<const uint4*>(p)[0], b = reinterpret_cast<const uint4*>(p)[1];
+    w[0] = a.x, w[1] = a.y, w[2] = a.z, w[3] = a.w, w[4] = b.x, w[5] = b.y, w[6] = b.z, w[7] = b.w;
+  }
+}
+
+// L2-coherent read (partials written by other SMs)
+__device__ __forceinline__ void load_u32x8_cg(const void* p, uint32_t* w) {
+  asm volatile("ld.global.cg.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]), "=r"(w[4]), "=r"(w[5]), "=r"(w[6]), "=r"(w[7])
+               : "l"(p)
+               : "memory");
+}
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+// Final write of 32 consecutive output columns of one row from fp32 values acc[32].
+__device__ __forceinline__ void write_chunk(const GemmParams& p, float alpha, int64_t row, int col, const float* acc) {
+  const int64_t idx = row * p.N + col;
+  if (p.out_kind == kOutBf16) {
+    uint32_t o[16];
+    if (p.resid != nullptr) {
+      uint32_t rw[16];
+      const auto* rp = static_cast<const __nv_bfloat16*>(p.resid) + idx;
+      load_u32x8(rp, rw, p.wide);
+      load_u32x8(rp + 16, rw + 8, p.wide);
+#pragma unroll
+      for (int k = 0; k < 16; ++k) {
+        // the reference's separate add: the GEMM's bf16 output, then bf16(x + r)
+        const float y0 = __bfloat162float(__float2bfloat16(acc[2 * k]));
+        const float y1 = __bfloat162float(__float2bfloat16(acc[2 * k + 1]));
+        o[k] = pack_bf16x2(y0 + __uint_as_float(rw[k] << 16), y1 + __uint_as_float(rw[k] & 0xffff0000u));
+      }
+    } else {
+#pragma unroll
+      for (int k = 0; k < 16; ++k)
+        o[k] = pack_bf16x2(acc[2 * k], acc[2 * k + 1]);
+    }
+    auto* dp = static_cast<__nv_bfloat16*>(p.d) + idx;
+    store_u32x8(dp, o, p.wide);
+    store_u32x8(dp + 16, o + 8, p.wide);
+  } else {
+    float* dp = static_cast<float*>(p.d) + idx;
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      uint32_t o[8];
+      if (p.accumulate) {
+        uint32_t old[8];
+        load_u32x8(dp + 8 * g, old, p.wide);
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          o[k] = __float_as_uint(fmaf(alpha, acc[8 * g + k], __uint_as_float(old[k])));
+      } else {
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          o[k] = __float_as_uint(alpha * acc[8 * g + k]);
+      }
+      store_u32x8(dp + 8 * g, o, p.wide);
+    }
+  }
+}
+
+template <int BN>
+__global__ void __launch_bounds__(kThreads, 1)
+      mxb200_mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                            const GemmParams p) {
+  using C = Config<BN>;
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  unsigned char* s_a = smem;
+  unsigned char* s_b = s_a + C::kStages * C::kABytes;
+  unsigned char* s_sf = s_b + C::kStages * C::kBBytes;  // per stage: A's tile, then B's tiles
+  Barriers* bars = reinterpret_cast<Barriers*>(s_sf + C::kStages * C::kSfBytes);
+
+  const int warp = static_cast<int>(threadIdx.x) >> 5, lane = static_cast<int>(threadIdx.x) & 31;
+  const int total_units = p.tiles_m * p.tiles_n * p.splits;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::kStages; ++s) {
+      mbar_init(&bars->full[s], 1);
+      mbar_init(&bars->empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&bars->tmem_full[a], 1);
+      mbar_init(&bars->tmem_empty[a], kEpilogueThreads);
+    }
+    mbar_init(&bars->overlap_free, kEpilogueThreads);
+    mbar_init(&bars->epi_sync, kEpilogueThreads);
+    bars->abort_flag = 0;
+    bars->last_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 0 && lane == 0) {
+    prefetch_tensormap(&map_a);
+    prefetch_tensormap(&map_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(&bars->tmem_base, kTmemCols);
+    tmem_relinquish();
+  }
+  tcgen05_fence_before_sync();
+  __syncthreads();
+  tcgen05_fence_after_sync();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&bars->tmem_base);
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int unit = blockIdx.x; ok && unit < total_units; unit += gridDim.x) {
+        const TileCoord tc = decode_unit(p, unit);
+        const int n_rows_left = p.N - tc.n * BN;
+        const int sfb_tiles = n_rows_left >= BN ? C::kSfbTiles : n_rows_left / 128;
+        const uint32_t tx = C::kABytes + C::kBBytes + kScaleTileBytes * (1 + sfb_tiles);
+        const int k_begin = tc.split * p.k_tiles_split;
+        const int k_end = min(k_begin + p.k_tiles_split, p.k_tiles_total);
+        const uint8_t* sfa_src = p.a_scale + static_cast<int64_t>(tc.m) * p.k_tiles_total * kScaleTileBytes;
+        const uint8_t* sfb_src = p.b_scale + static_cast<int64_t>(tc.n) * C::kSfbTiles * p.k_tiles_total * kScaleTileBytes;
+        for (int kt = k_begin; kt < k_end; ++kt) {
+          if (!wait_bounded(&bars->empty[stage], phase ^ 1u, bars, kSiteProducerEmpty)) {
+            ok = false;
+            break;
+          }
+          uint64_t* full = &bars->full[stage];
+          mbar_arrive_expect_tx(full, tx);
+          tma_load_2d(s_a + stage * C::kABytes, &map_a, full, kt * kBK, tc.m * kBM);
+          tma_load_2d(s_b + stage * C::kBBytes, &map_b, full, kt * kBK, tc.n * BN);
+          unsigned char* sf = s_sf + stage * C::kSfBytes;
+          bulk_load(sf, sfa_src + static_cast<int64_t>(kt) * kScaleTileBytes, kScaleTileBytes, full);
+          for (int j = 0; j < sfb_tiles; ++j)
+            bulk_load(sf + (1 + j) * kScaleTileBytes,
+                      sfb_src + (static_cast<int64_t>(j) * p.k_tiles_total + kt) * kScaleTileBytes, kScaleTileBytes,
+                      full);
+          if (++stage == C::kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      uint32_t local = 0;  // tiles this CTA has started
+      bool ok = true;
+      const uint32_t sfa_t = tmem_base + C::kSfaCol, sfb_t = tmem_base + C::kSfbCol;
+      for (int unit = blockIdx.x; ok && unit < total_units; unit += gridDim.x, ++local) {
+        const TileCoord tc = decode_unit(p, unit);
+        const int n_rows_left = p.N - tc.n * BN;
+        const int n_valid = n_rows_left >= BN ? BN : n_rows_left;
+        const int sfb_tiles = n_valid / 128;
+        const uint32_t idesc = make_idesc_mxf8(kBM, static_cast<uint32_t>(n_valid));
+        const uint32_t buf = local & 1u, use = local >> 1;
+        // the buffer's previous tile (two tiles ago) must be drained ...
+        if (!wait_bounded(&bars->tmem_empty[buf], (use & 1u) ^ 1u, bars, kSiteMmaTmemEmpty)) {
+          ok = false;
+          break;
+        }
+        // ... and, with overlapping buffers, the previous tile must have given up the shared columns
+        if (C::kOverlap && local > 0) {
+          if (!wait_bounded(&bars->overlap_free, (local - 1) & 1u, bars, kSiteMmaOverlap)) {
+            ok = false;
+            break;
+          }
+        }
+        tcgen05_fence_after_sync();
+        const uint32_t acc_t = tmem_base + (buf ? C::kAcc1 : C::kAcc0);
+        const int k_begin = tc.split * p.k_tiles_split;
+        const int k_end = min(k_begin + p.k_tiles_split, p.k_tiles_total);
+        for (int kt = k_begin; kt < k_end; ++kt) {
+          if (!wait_bounded(&bars->full[stage], phase, bars, kSiteMmaFull)) {
+            ok = false;
+            break;
+          }
+          tcgen05_fence_after_sync();
+          const uint32_t sf_addr = smem_u32(s_sf + stage * C::kSfBytes);
+          // scale tiles: 32 rows x 16 bytes, 8-row groups 128 bytes apart, no swizzle
+          tcgen05_cp_32x128b_warpx4(sfa_t, make_smem_desc(sf_addr, 0, 128, 0));
+          for (int j = 0; j < sfb_tiles; ++j)
+            tcgen05_cp_32x128b_warpx4(sfb_t + 4 * j, make_smem_desc(sf_addr + (1 + j) * kScaleTileBytes, 0, 128, 0));
+          // operand tiles: K-major, 128-byte swizzle, 8-row groups 1024 bytes apart
+          const uint64_t a_desc = make_smem_desc(smem_u32(s_a + stage * C::kABytes), 16, 1024, 2);
+          const uint64_t b_desc = make_smem_desc(smem_u32(s_b + stage * C::kBBytes), 16, 1024, 2);
+#pragma unroll
+          for (uint32_t k = 0; k < 4; ++k) {
+            // K = 32 per step: 32 bytes further into the swizzle atom; scale byte k of the 32-bit column
+            tcgen05_mma_mxf8(acc_t, a_desc + 2 * k, b_desc + 2 * k, idesc_with_sf(idesc, k, k), sfa_t, sfb_t,
+                             (kt > k_begin || k > 0) ? 1u : 0u);
+          }
+          tcgen05_commit(&bars->empty[stage]);
+          if (++stage == C::kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (ok)
+          tcgen05_commit(&bars->tmem_full[buf]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..5)
+    const int quarter = warp & 3;  // the TMEM lanes this warp may read: 32 * (warp id % 4) ...
+    const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
+    const float alpha = (p.out_kind == kOutF32 && p.alpha != nullptr) ? *p.alpha : 1.f;
+    uint32_t local = 0, sync_phase = 0;
+    bool ok = true;
+    constexpr int kChunks = BN / 32;
+    for (int unit = blockIdx.x; ok && unit < total_units; unit += gridDim.x, ++local) {
+      const TileCoord tc = decode_unit(p, unit);
+      const uint32_t buf = local & 1u, use = local >> 1;
+      if (!wait_bounded(&bars->tmem_full[buf], use & 1u, bars, kSiteEpilogueFull)) {
+        ok = false;
+        break;
+      }
+      tcgen05_fence_after_sync();
+      const uint32_t acc_t = tmem_base + lane_base + (buf ? C::kAcc1 : C::kAcc0);
+      const int64_t row = static_cast<int64_t>(tc.m) * kBM + quarter * 32 + lane;
+      const int col0 = tc.n * BN;
+      float* part = p.splits > 1
+                          ? p.partials + (static_cast<int64_t>(tc.tile) * p.splits + tc.split) * (kBM * BN) +
+                                  static_cast<int64_t>(quarter * 32 + lane) * BN
+                          : nullptr;
+#pragma unroll 1
+      for (int i = 0; i < kChunks; ++i) {
+        // overlapping buffers: buffer 0 shares its last 32 columns, buffer 1 its first 32; drain those first
+        const int c = (C::kOverlap && buf == 0) ? (i == 0 ? kChunks - 1 : i - 1) : i;
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(acc_t + c * 32, r);
+        tmem_ld_wait();
+        if (C::kOverlap && i == 0) {
+          tcgen05_fence_before_sync();
+          mbar_arrive(&bars->overlap_free);
+        }
+        if (col0 + c * 32 < p.N) {
+          if (part != nullptr) {
+#pragma unroll
+            for (int g = 0; g < 4; ++g)
+              store_u32x8(part + c * 32 + 8 * g, r + 8 * g, true);
+          } else {
+            write_chunk(p, alpha, row, col0 + c * 32, reinterpret_cast<const float*>(r));
+          }
+        }
+      }
+      tcgen05_fence_before_sync();
+      mbar_arrive(&bars->tmem_empty[buf]);
+
+      if (part != nullptr) {
+        // split-K: publish this slice, then the last CTA to arrive for the tile sums all slices in order
+        __threadfence();
+        mbar_arrive(&bars->epi_sync);
+        if (!wait_bounded(&bars->epi_sync, sync_phase, bars, kSiteEpilogueSync)) {
+          ok = false;
+          break;
+        }
+        sync_phase ^= 1u;
+        if (threadIdx.x == 64) {
+          const uint32_t prev = atomicAdd(&p.counters[tc.tile], 1u);
+          const bool last = prev + 1 == static_cast<uint32_t>(p.splits);
+          if (last)
+            p.counters[tc.tile] = 0;  // ready for the next call
+          *reinterpret_cast<volatile uint32_t*>(&bars->last_flag) = last ? 1u : 0u;
+        }
+        mbar_arrive(&bars->epi_sync);
+        if (!wait_bounded(&bars->epi_sync, sync_phase, bars, kSiteEpilogueSync)) {
+          ok = false;
+          break;
+        }
+        sync_phase ^= 1u;
+        const bool last = *reinterpret_cast<volatile uint32_t*>(&bars->last_flag) != 0;
+        if (last) {
+          __threadfence();
+          const float* tile_part = p.partials + static_cast<int64_t>(tc.tile) * p.splits * (kBM * BN) +
+                                   static_cast<int64_t>(quarter * 32 + lane) * BN;
+#pragma unroll 1
+          for (int c = 0; c < kChunks; ++c) {
+            if (col0 + c * 32 >= p.N)
+              break;
+            float acc[32];
+#pragma unroll
+            for (int k = 0; k < 32; ++k)
+              acc[k] = 0.f;
+            for (int s = 0; s < p.splits; ++s) {
+              const float* src = tile_part + static_cast<int64_t>(s) * (kBM * BN) + c * 32;
+#pragma unroll
+              for (int g = 0; g < 4; ++g) {
+                uint32_t w[8];
+                load_u32x8_cg(src + 8 * g, w);
+#pragma unroll
+                for (int k = 0; k < 8; ++k)
+                  acc[8 * g + k] += __uint_as_float(w[k]);
+              }
+            }
+            write_chunk(p, alpha, row, col0 + c * 32, acc);
+          }
+        }
+        // the flag is rewritten only after every thread has read it
+        mbar_arrive(&bars->epi_sync);
+        if (!wait_bounded(&bars->epi_sync, sync_phase, bars, kSiteEpilogueSync)) {
+          ok = false;
+          break;
+        }
+        sync_phase ^= 1u;
+      }
+    }
+  }
+
+  // teardown: on an abort give copies and MMAs in flight time to land before shared and tensor memory go away
+  if (*reinterpret_cast<volatile uint32_t*>(&bars->abort_flag) != 0) {
+    const uint64_t t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 200000ull) {
+    }
+  }
+  tcgen05_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tcgen05_fence_after_sync();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ host side
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = [] {
+    void* f = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      f = nullptr;
+    return reinterpret_cast<EncodeTiledFn>(f);
+  }();
+  return fn;
+}
+
+// (rows, k) row-major bytes, box = box_rows x 128 bytes, 128-byte swizzle
+int make_operand_map(CUtensorMap* map, const void* base, int64_t rows, int64_t k, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr)
+    return MXB200_ERR_DRIVER;
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(k), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(k)};
+  const cuuint32_t box[2] = {static_cast<cuuint32_t>(kBK), static_cast<cuuint32_t>(box_rows)};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? MXB200_OK : MXB200_ERR_DRIVER;
+}
+
+std::atomic<int> g_tile_n{0};
+std::atomic<int> g_max_ctas{0};
+
+int choose_bn(int64_t N) {
+  const int forced = g_tile_n.load();
+  if (forced == 128 || forced == 256)
+    return forced;
+  return N >= 256 ? 256 : 128;
+}
+
+template <int BN>
+int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, int grid, cudaStream_t stream) {
+  static std::mutex mu;
+  static bool configured[64] = {};
+  int device = 0;
+  cudaGetDevice(&device);
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (device < 64 && !configured[device]) {
+      if (cudaFuncSetAttribute(mxb200_mx_gemm_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               static_cast<int>(Config<BN>::kSmemBytes)) != cudaSuccess)
+        return MXB200_ERR_LAUNCH;
+      configured[device] = true;
+    }
+  }
+  mxb200_mx_gemm_kernel<BN><<<grid, kThreads, Config<BN>::kSmemBytes, stream>>>(ma, mb, p);
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return launch_status();
+}
+
+size_t counters_bytes(int64_t tiles) {
+  return static_cast<size_t>((tiles * 4 + 255) / 256 * 256);
+}
+
+int gemm(const void* a, const void* a_scale, const void* b, const void* b_scale, void* d, int out_kind,
+         const void* resid, int64_t M, int64_t N, int64_t K, const float* alpha, int accumulate, int splits,
+         void* workspace, size_t workspace_bytes, void* stream) {
+  DeviceInfo dev;
+  if (int s = current_device(&dev); s != MXB200_OK)
+    return s;
+  if (a == nullptr || a_scale == nullptr || b == nullptr || b_scale == nullptr || d == nullptr)
+    return MXB200_ERR_NULL;
+  if (M <= 0 || N <= 0 || K <= 0 || M % 128 != 0 || N % 128 != 0 || K % 128 != 0 || M > (1 << 30) || N > (1 << 30) ||
+      K > (1 << 30))
+    return MXB200_ERR_SHAPE;
+  if (!aligned16(a) || !aligned16(a_scale) || !aligned16(b) || !aligned16(b_scale) || !aligned16(d) ||
+      (resid != nullptr && !aligned16(resid)))
+    return MXB200_ERR_ALIGNMENT;
+  if (out_kind != kOutBf16 && out_kind != kOutF32)
+    return MXB200_ERR_ARGUMENT;
+  if (out_kind == kOutF32 && resid != nullptr)
+    return MXB200_ERR_ARGUMENT;
+  const int k_tiles = static_cast<int>(K / kBK);
+  if (splits < 1 || splits > k_tiles || splits > 64)
+    return MXB200_ERR_ARGUMENT;
+
+  const int bn = choose_bn(N);
+  GemmParams p{};
+  p.a_scale = static_cast<const uint8_t*>(a_scale);
+  p.b_scale = static_cast<const uint8_t*>(b_scale);
+  p.d = d;
+  p.resid = out_kind == kOutBf16 ? resid : nullptr;
+  p.alpha = out_kind == kOutF32 ? alpha : nullptr;
+  p.M = static_cast<int>(M), p.N = static_cast<int>(N), p.K = static_cast<int>(K);
+  p.tiles_m = static_cast<int>(M / kBM);
+  p.tiles_n = static_cast<int>((N + bn - 1) / bn);
+  p.k_tiles_total = k_tiles;
+  p.k_tiles_split = (k_tiles + splits - 1) / splits;
+  p.splits = (k_tiles + p.k_tiles_split - 1) / p.k_tiles_split;  // no empty slices
+  p.panel = std::min(p.tiles_n, 8);
+  p.out_kind = out_kind;
+  p.accumulate = out_kind == kOutF32 ? (accumulate != 0) : 0;
+  p.wide = (reinterpret_cast<uintptr_t>(d) & 31u) == 0 && (reinterpret_cast<uintptr_t>(resid) & 31u) == 0;
+  const int64_t tiles = static_cast<int64_t>(p.tiles_m) * p.tiles_n;
+  if (tiles * p.splits > 0x7fffffffLL)
+    return MXB200_ERR_SHAPE;
+  auto* s = static_cast<cudaStream_t>(stream);
+  if (p.splits > 1) {
+    const size_t need = counters_bytes(tiles) + static_cast<size_t>(tiles) * p.splits * kBM * bn * sizeof(float);
+    if (workspace == nullptr || workspace_bytes < need)
+      return MXB200_ERR_WORKSPACE;
+    if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0)
+      return MXB200_ERR_ALIGNMENT;
+    p.counters = static_cast<uint32_t*>(workspace);
+    p.partials = reinterpret_cast<float*>(static_cast<unsigned char*>(workspace) + counters_bytes(tiles));
+    if (cudaMemsetAsync(p.counters, 0, counters_bytes(tiles), s) != cudaSuccess)
+      return MXB200_ERR_LAUNCH;
+  }
+  CUtensorMap ma, mb;
+  if (int st = make_operand_map(&ma, a, M, K, kBM); st != MXB200_OK)
+    return st;
+  if (int st = make_operand_map(&mb, b, N, K, bn); st != MXB200_OK)
+    return st;
+  const int cap = g_max_ctas.load() > 0 ? g_max_ctas.load() : dev.sms;
+  const int grid = static_cast<int>(std::min<int64_t>(tiles * p.splits, cap));
+  return bn == 256 ? launch<256>(ma, mb, p, grid, s) : launch<128>(ma, mb, p, grid, s);
+}
+
+}  // namespace
+
+}  // namespace mxb200
+
+extern "C" int mxb200_gemm_bf16(const void* a, const void* a_scale, const void* b, const void* b_scale, void* d,
+                                const void* resid, int64_t M, int64_t N, int64_t K, void* stream) {
+  return mxb200::gemm(a, a_scale, b, b_scale, d, mxb200::kOutBf16, resid, M, N, K, nullptr, 0, 1, nullptr, 0, stream);
+}
+
+extern "C" int mxb200_gemm_f32(const void* a, const void* a_scale, const void* b, const void* b_scale, float* d,
+                               int64_t M, int64_t N, int64_t K, const float* alpha, int accumulate, void* stream) {
+  return mxb200::gemm(a, a_scale, b, b_scale, d, mxb200::kOutF32, nullptr, M, N, K, alpha, accumulate, 1, nullptr, 0,
+                      stream);
+}
+
+extern "C" int mxb200_gemm_splits(int64_t M, int64_t N, int64_t K) {
+  mxb200::DeviceInfo dev;
+  if (mxb200::current_device(&dev) != MXB200_OK || M <= 0 || N <= 0 || K <= 0)
+    return 1;
+  const int bn = mxb200::choose_bn(N);
+  const int64_t tiles = (M / 128) * ((N + bn - 1) / bn);
+  const int64_t k_tiles = K / 128;
+  // split only while a single wave leaves SMs idle and every slice keeps a deep main loop
+  int best = 1;
+  double best_eff = 0.0;
+  for (int s = 1; s <= 8; ++s) {
+    if (k_tiles / s < 16 && s > 1)
+      break;
+    const int64_t units = tiles * s;
+    const int64_t waves = (units + dev.sms - 1) / dev.sms;
+    const double eff = static_cast<double>(units) / static_cast<double>(waves * dev.sms) * (s == 1 ? 1.0 : 0.97);
+    if (eff > best_eff + 0.02) {
+      best_eff = eff;
+      best = s;
+    }
+  }
+  return best;
+}
+
+extern "C" size_t mxb200_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int splits) {
+  (void)K;
+  if (splits <= 1 || M <= 0 || N <= 0)
+    return 0;
+  const int bn = mxb200::choose_bn(N);
+  const int64_t tiles = (M / 128) * ((N + bn - 1) / bn);
+  return mxb200::counters_bytes(tiles) + static_cast<size_t>(tiles) * splits * 128 * bn * sizeof(float);
+}
+
+extern "C" int mxb200_gemm_splitk(const void* a, const void* a_scale, const void* b, const void* b_scale, void* d,
+                                  int out_kind, const void* resid, int64_t M, int64_t N, int64_t K, const float* alpha,
+                                  int accumulate, int splits, void* workspace, size_t workspace_bytes, void* stream) {
+  return mxb200::gemm(a, a_scale, b, b_scale, d, out_kind, resid, M, N, K, alpha, accumulate, splits, workspace,
+                      workspace_bytes, stream);
+}
+
+extern "C" int mxb200_set_gemm_config(int tile_n, int max_ctas) {
+  if ((tile_n != 0 && tile_n != 128 && tile_n != 256) || max_ctas < 0)
+    return MXB200_ERR_ARGUMENT;
+  mxb200::g_tile_n.store(tile_n);
+  mxb200::g_max_ctas.store(max_ctas);
+  return MXB200_OK;
+}
+
+extern "C" int mxb200_device_status(uint32_t* word) {
+  uint32_t w = 0;
+  if (cudaDeviceSynchronize() != cudaSuccess)
+    return MXB200_ERR_LAUNCH;
+  if (cudaMemcpyFromSymbol(&w, mxb200::g_watchdog_word, sizeof(w)) != cudaSuccess)
+    return MXB200_ERR_LAUNCH;
+  if (w != 0) {
+    const uint32_t zero = 0;
+    cudaMemcpyToSymbol(mxb200::g_watchdog_word, &zero, sizeof(zero));
+  }
+  if (word != nullptr)
+    *word = w;
+  return w == 0 ? MXB200_OK : MXB200_ERR_WATCHDOG;
+}

@@ -1,0 +1,365 @@
+"""Host-side mirror of nanochat-cpp's MXFP8 Linear interface over libmxb200.so.
+
+Same names, argument meaning and error behaviour as the reference's fp8.h / mx_gemm.h (file:line cited per
+function, paths within nanochat-cpp), with torch tensors used only as owners of device memory. Every call
+goes to the CUDA library through the C ABI; nothing here computes on the CPU and nothing falls back.
+"""
+from __future__ import annotations
+
+import enum
+from dataclasses import dataclass
+from typing import Callable, List, Optional, Sequence
+
+import torch
+
+from . import capi
+from .capi import MxOut, check, lib
+
+__all__ = [
+    "Fp8Tensor", "Fp8WeightCache", "MxGemmBackend", "set_mx_gemm_backend", "mx_gemm_backend", "mx_fits",
+    "empty_mx", "empty_mx_scale", "mx_out", "mx_outs", "quantize_mx", "quantize_mx_into",
+    "quantize_mx_relu_square_bwd", "quantize_fp8_weight", "mx_qkv_weights", "mx_gemm", "mx_gemm_out",
+    "mx_gemm_f32", "mx_grad_direct", "mx_grad_weights", "fp8_matmul", "fp8_eligible",
+    "SCALE_REFERENCE", "SCALE_OCP_FLOOR",
+]
+
+SCALE_REFERENCE = capi.SCALE_REFERENCE
+SCALE_OCP_FLOOR = capi.SCALE_OCP_FLOOR
+E4M3 = torch.float8_e4m3fn
+E8M0 = torch.float8_e8m0fnu
+
+
+class MxGemmBackend(enum.Enum):
+    """src/nanochat/model/fp8/mx_gemm.h:9 has {Cublas, Cutlass}; this library is the third value a
+    ``--gemm=b200`` flag would select. It is the only one implemented here."""
+    B200 = "b200"
+
+
+_backend = MxGemmBackend.B200
+
+
+def set_mx_gemm_backend(backend: MxGemmBackend) -> None:
+    """src/nanochat/model/fp8/mx_gemm.cpp:134-136. Anything but B200 raises: there is no other backend."""
+    global _backend
+    if backend is not MxGemmBackend.B200:
+        raise ValueError("only MxGemmBackend.B200 exists in this library")
+    _backend = backend
+
+
+def mx_gemm_backend() -> MxGemmBackend:
+    return _backend
+
+
+@dataclass
+class Fp8Tensor:
+    """A quantized 2-D tensor: data (R, C) scaled along its rows, data_t (C, R) scaled along its own rows,
+    swizzled E8M0 scales for each (src/nanochat/model/fp8/fp8.h:68-77)."""
+    data: Optional[torch.Tensor] = None
+    data_t: Optional[torch.Tensor] = None
+    inv_scale: Optional[torch.Tensor] = None
+    inv_scale_t: Optional[torch.Tensor] = None
+
+
+def mx_fits(rows: int, cols: int) -> bool:
+    """src/nanochat/model/fp8/fp8.h:86-88."""
+    return rows % 128 == 0 and cols % 128 == 0
+
+
+def fp8_eligible(in_features: int, out_features: int) -> bool:
+    """src/nanochat/model/fp8/fp8.h:127-130."""
+    return in_features % 16 == 0 and out_features % 16 == 0 and min(in_features, out_features) >= 128
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _require_cuda(t: torch.Tensor, what: str) -> None:
+    if not t.is_cuda:
+        raise RuntimeError(f"{what}: expected a CUDA tensor; this engine has no CPU path")
+
+
+def empty_mx_scale(rows: int, cols: int, device) -> torch.Tensor:
+    """src/nanochat/model/fp8/fp8.cpp:113-115."""
+    return torch.empty(rows * cols // 32, dtype=E8M0, device=device)
+
+
+def empty_mx(R: int, C: int, device, rows: bool = True, cols: bool = True) -> Fp8Tensor:
+    """src/nanochat/model/fp8/fp8.cpp:122-133."""
+    q = Fp8Tensor()
+    if rows:
+        q.data = torch.empty((R, C), dtype=E4M3, device=device)
+        q.inv_scale = empty_mx_scale(R, C, device)
+    if cols:
+        q.data_t = torch.empty((C, R), dtype=E4M3, device=device)
+        q.inv_scale_t = empty_mx_scale(C, R, device)
+    return q
+
+
+def mx_out(data: torch.Tensor, scale: torch.Tensor, row: int = 0, col: int = 0) -> MxOut:
+    """The kernels' view of MX data (R, ld) from (row, col) on; row, col % 128 == 0
+    (src/nanochat/model/fp8/fp8.cpp:117-120)."""
+    if row % 128 or col % 128:
+        raise RuntimeError("mx_out: row and col must be multiples of 128")
+    ld = data.size(1)
+    tiles = ld // 128
+    return MxOut(data.data_ptr() + row * ld + col, ld, scale.data_ptr() + ((row // 128) * tiles + col // 128) * 512, tiles)
+
+
+def mx_outs(q: Fp8Tensor):
+    """src/nanochat/model/fp8/fp8.cpp:135-142."""
+    out = mx_out(q.data, q.inv_scale) if q.data is not None else MxOut(None, 0, None, 0)
+    out_t = mx_out(q.data_t, q.inv_scale_t) if q.data_t is not None else MxOut(None, 0, None, 0)
+    return out, out_t
+
+
+def quantize_mx_into(x: torch.Tensor, relu_square: bool, out: MxOut, out_t: MxOut,
+                     scale_rule: int = SCALE_REFERENCE) -> None:
+    """quantize_mx of x into given buffers (src/nanochat/model/fp8/fp8.cpp:144-153)."""
+    _require_cuda(x, "quantize_mx")
+    if not (x.dim() == 2 and x.is_contiguous() and mx_fits(x.size(0), x.size(1))
+            and x.dtype in (torch.bfloat16, torch.float32) and (not relu_square or x.dtype == torch.bfloat16)):
+        raise RuntimeError("MX: expected an aligned, contiguous 2D tensor with dims % 128")
+    check(lib.mxb200_quantize_mx(x.data_ptr(), int(x.dtype == torch.bfloat16), x.size(0), x.size(1), out, out_t,
+                                 capi.PROLOGUE_RELU_SQUARE if relu_square else capi.PROLOGUE_NONE, scale_rule,
+                                 _stream()), "quantize_mx")
+
+
+def quantize_mx(x: torch.Tensor, rows: bool = True, cols: bool = True, relu_square: bool = False,
+                scale_rule: int = SCALE_REFERENCE) -> Fp8Tensor:
+    """MXFP8 E4M3 of a contiguous 2-D bf16 or fp32 x (src/nanochat/model/fp8/fp8.h:82-84,
+    fp8.cpp:538-549)."""
+    _require_cuda(x, "quantize_mx")
+    q = empty_mx(x.size(0), x.size(1), x.device, rows, cols)
+    out, out_t = mx_outs(q)
+    quantize_mx_into(x, relu_square, out, out_t, scale_rule)
+    return q
+
+
+def quantize_mx_relu_square_bwd(g: torch.Tensor, h: torch.Tensor, rows: bool = True, cols: bool = True,
+                                scale_rule: int = SCALE_REFERENCE) -> Fp8Tensor:
+    """MX of dh = bf16(h > 0 ? g * 2h : 0) without writing dh
+    (src/nanochat/model/fp8/fp8_kernel.h:41-43; caller fp8.cpp:318-323)."""
+    _require_cuda(g, "quantize_mx_relu_square_bwd")
+    if not (g.shape == h.shape and g.dtype == h.dtype == torch.bfloat16 and g.is_contiguous() and h.is_contiguous()
+            and mx_fits(g.size(0), g.size(1))):
+        raise RuntimeError("MX: expected two contiguous bf16 2D tensors of one shape with dims % 128")
+    q = empty_mx(g.size(0), g.size(1), g.device, rows, cols)
+    out, out_t = mx_outs(q)
+    check(lib.mxb200_quantize_mx_relu_square_bwd(g.data_ptr(), h.data_ptr(), g.size(0), g.size(1), out, out_t,
+                                                 scale_rule, _stream()), "quantize_mx_relu_square_bwd")
+    return q
+
+
+class Fp8WeightCache:
+    """FP8 copies of weights, remade only when a weight changes: in-place updates bump the tensor's version
+    (src/nanochat/model/fp8/fp8.h:18-38, fp8.cpp:516-536)."""
+
+    def __init__(self, enabled: bool = False):
+        self.enabled = enabled
+        self._kind = -1
+        self._keys: list = []
+        self._value: list = []
+
+    def get(self, kind: int, weights: Sequence[torch.Tensor], make: Callable[[], List[torch.Tensor]]):
+        if not self.enabled:
+            return make()
+        keys = [(id(w), w.data_ptr(), w._version) for w in weights]
+        if kind != self._kind or keys != self._keys:
+            self._value = make()
+            self._kind, self._keys = kind, keys
+        return self._value
+
+
+def quantize_fp8_weight(w: torch.Tensor, cache: Optional[Fp8WeightCache] = None) -> Fp8Tensor:
+    """A weight's E4M3 copy under MX, from cache while w is unchanged
+    (src/nanochat/model/fp8/fp8.cpp:551-558)."""
+    def make():
+        q = quantize_mx(w.detach().contiguous())
+        return [q.data, q.data_t, q.inv_scale, q.inv_scale_t]
+    v = cache.get(1, [w], make) if cache is not None else make()
+    return Fp8Tensor(v[0], v[1], v[2], v[3])
+
+
+def mx_qkv_weights(wq: torch.Tensor, wk: torch.Tensor, wv: torch.Tensor, cache: Optional[Fp8WeightCache] = None):
+    """Merged q/k/v weights: {w_cat (n, C), w_cat^T (C, n), their scales}; each part quantized into its row
+    range of one buffer (src/nanochat/model/fp8/fp8.cpp:155-171)."""
+    C = wq.size(1)
+    n = wq.size(0) + wk.size(0) + wv.size(0)
+
+    def make():
+        out = [torch.empty((n, C), dtype=E4M3, device=wq.device), torch.empty((C, n), dtype=E4M3, device=wq.device),
+               empty_mx_scale(n, C, wq.device), empty_mx_scale(C, n, wq.device)]
+        row = 0
+        for w in (wq, wk, wv):
+            if w.size(1) != C:
+                raise RuntimeError("q/k/v weights must share the input dim")
+            quantize_mx_into(w.detach().contiguous(), False, mx_out(out[0], out[2], row, 0), mx_out(out[1], out[3], 0, row))
+            row += w.size(0)
+        return out
+    return cache.get(1, [wq, wk, wv], make) if cache is not None else make()
+
+
+# ------------------------------------------------------------------------------------------------ GEMMs
+
+_workspaces: dict = {}
+
+
+def _workspace(device, nbytes: int) -> torch.Tensor:
+    """Split-K scratch, grown on demand and kept per device (the reference's cuBLASLt path likewise borrows
+    torch's workspace, src/nanochat/model/fp8/mx_gemm.cpp:236-237)."""
+    key = (device.type, device.index if device.index is not None else torch.cuda.current_device())
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _workspaces[key] = ws
+    return ws
+
+
+def _check_operands(a, a_scale, b, b_scale, what):
+    for t in (a, a_scale, b, b_scale):
+        _require_cuda(t, what)
+    if not (a.dim() == 2 and b.dim() == 2 and a.is_contiguous() and b.is_contiguous() and a.dtype == E4M3
+            and b.dtype == E4M3 and a.size(1) == b.size(1)):
+        raise RuntimeError(f"{what}: shape mismatch")
+    M, N, K = a.size(0), b.size(0), a.size(1)
+    if a_scale.numel() != M * K // 32 or b_scale.numel() != N * K // 32:
+        raise RuntimeError(f"{what}: expected e4m3 operands with their MX scales")
+    return M, N, K
+
+
+def mx_gemm_out(out: torch.Tensor, a: torch.Tensor, a_scale: torch.Tensor, b: torch.Tensor, b_scale: torch.Tensor,
+                resid: Optional[torch.Tensor] = None, splits: Optional[int] = None) -> None:
+    """mx_gemm into out, bf16 or fp32 (src/nanochat/model/fp8/mx_gemm.h:26-27, mx_gemm.cpp:164-173).
+    resid: optional bf16 (M, N) residual fused into the bf16 epilogue. splits: None lets the library decide."""
+    M, N, K = _check_operands(a, a_scale, b, b_scale, "mx_gemm")
+    if not (out.is_contiguous() and out.size(0) == M and out.size(1) == N and out.dtype in (torch.bfloat16, torch.float32)):
+        raise RuntimeError("mx_gemm: shape mismatch")
+    kind = capi.OUT_BF16 if out.dtype == torch.bfloat16 else capi.OUT_F32
+    if resid is not None and not (kind == capi.OUT_BF16 and resid.shape == out.shape and resid.dtype == torch.bfloat16
+                                  and resid.is_contiguous()):
+        raise RuntimeError("mx_gemm: the residual must be a contiguous bf16 tensor of the output's shape")
+    s = lib.mxb200_gemm_splits(M, N, K) if splits is None else splits
+    rp = resid.data_ptr() if resid is not None else None
+    if s <= 1:
+        if kind == capi.OUT_BF16:
+            st = lib.mxb200_gemm_bf16(a.data_ptr(), a_scale.data_ptr(), b.data_ptr(), b_scale.data_ptr(), out.data_ptr(),
+                                      rp, M, N, K, _stream())
+        else:
+            st = lib.mxb200_gemm_f32(a.data_ptr(), a_scale.data_ptr(), b.data_ptr(), b_scale.data_ptr(), out.data_ptr(),
+                                     M, N, K, None, 0, _stream())
+    else:
+        nbytes = lib.mxb200_gemm_workspace_bytes(M, N, K, s)
+        ws = _workspace(out.device, nbytes)
+        st = lib.mxb200_gemm_splitk(a.data_ptr(), a_scale.data_ptr(), b.data_ptr(), b_scale.data_ptr(), out.data_ptr(),
+                                    kind, rp, M, N, K, None, 0, s, ws.data_ptr(), ws.numel(), _stream())
+    check(st, "mx_gemm")
+
+
+def mx_gemm(a: torch.Tensor, a_scale: torch.Tensor, b: torch.Tensor, b_scale: torch.Tensor,
+            out_dtype: torch.dtype = torch.bfloat16, resid: Optional[torch.Tensor] = None,
+            splits: Optional[int] = None) -> torch.Tensor:
+    """a (M, K) . b (N, K)^T as out_dtype (src/nanochat/model/fp8/mx_gemm.h:18-24, mx_gemm.cpp:154-162)."""
+    out = torch.empty((a.size(0), b.size(0)), dtype=out_dtype, device=a.device)
+    mx_gemm_out(out, a, a_scale, b, b_scale, resid, splits)
+    return out
+
+
+def mx_gemm_f32(a: torch.Tensor, a_scale: torch.Tensor, b: torch.Tensor, b_scale: torch.Tensor, out: torch.Tensor,
+                accumulate: bool, alpha: Optional[torch.Tensor] = None, splits: Optional[int] = None) -> None:
+    """out (M, N) fp32 (+)= alpha * a . b^T; alpha a device fp32 scalar (None: 1)
+    (src/nanochat/model/fp8/mx_gemm.h:44-50, mx_gemm.cpp:214-319)."""
+    M, N, K = _check_operands(a, a_scale, b, b_scale, "mx_gemm_f32")
+    if not (out.is_cuda and out.is_contiguous() and out.dtype == torch.float32 and out.size(0) == M and out.size(1) == N):
+        raise RuntimeError("mx_gemm_f32: expected a contiguous fp32 (M, N) output")
+    if alpha is not None and not (alpha.is_cuda and alpha.dtype == torch.float32 and alpha.numel() == 1):
+        raise RuntimeError("mx_gemm_f32: alpha must be a device fp32 scalar")
+    ap = alpha.data_ptr() if alpha is not None else None
+    s = lib.mxb200_gemm_splits(M, N, K) if splits is None else splits
+    if s <= 1:
+        st = lib.mxb200_gemm_f32(a.data_ptr(), a_scale.data_ptr(), b.data_ptr(), b_scale.data_ptr(), out.data_ptr(),
+                                 M, N, K, ap, int(accumulate), _stream())
+    else:
+        nbytes = lib.mxb200_gemm_workspace_bytes(M, N, K, s)
+        ws = _workspace(out.device, nbytes)
+        st = lib.mxb200_gemm_splitk(a.data_ptr(), a_scale.data_ptr(), b.data_ptr(), b_scale.data_ptr(), out.data_ptr(),
+                                    capi.OUT_F32, None, M, N, K, ap, int(accumulate), s, ws.data_ptr(), ws.numel(),
+                                    _stream())
+    check(st, "mx_gemm_f32")
+
+
+# ------------------------------------------------------------------------------------------------ Linear
+
+def mx_grad_direct(w: torch.Tensor) -> bool:
+    """Whether backward may write w's gradient straight into w.grad: a contiguous fp32 leaf that requires
+    grad (src/nanochat/model/fp8/fp8.h:114-116)."""
+    return w.is_leaf and w.requires_grad and w.dtype == torch.float32 and w.is_contiguous()
+
+
+def mx_grad_weights(go_t: torch.Tensor, go_scale_t: torch.Tensor, in_t: torch.Tensor, in_scale_t: torch.Tensor,
+                    ws: Sequence[torch.Tensor], alpha: Optional[torch.Tensor] = None) -> None:
+    """dW = alpha * go_t (n, N) . in_t (C, N)^T into the .grad of ws, whose rows concatenate to n: allocated (=)
+    when undefined, else accumulated (+=). Several ws share one buffer, so one GEMM serves
+    (src/nanochat/model/fp8/fp8.h:118-125, fp8.cpp:470-514)."""
+    n, C = go_t.size(0), in_t.size(0)
+    if sum(w.size(0) for w in ws) != n or any(w.size(1) != C for w in ws):
+        raise RuntimeError("mx_grad_weights: weight rows must concatenate to the gradient's")
+    merged = None
+    if all(w.grad is not None for w in ws):
+        g0 = ws[0].grad
+        base = g0.data_ptr()
+        contiguous, row = True, 0
+        for w in ws:
+            contiguous &= w.grad.data_ptr() == base + row * C * 4 and w.grad.is_contiguous() and w.grad.dtype == torch.float32
+            row += w.size(0)
+        if contiguous and len(ws) > 1 and g0._base is not None and g0._base.numel() == n * C:
+            merged = g0._base.view(n, C)
+        elif contiguous and len(ws) == 1:
+            merged = g0
+    if merged is not None:
+        mx_gemm_f32(go_t, go_scale_t, in_t, in_scale_t, merged, True, alpha)
+        return
+    buf = torch.empty((n, C), dtype=torch.float32, device=go_t.device)
+    mx_gemm_f32(go_t, go_scale_t, in_t, in_scale_t, buf, False, alpha)
+    row = 0
+    for w in ws:
+        part = buf.narrow(0, row, w.size(0))
+        if w.grad is None:
+            w.grad = part  # row blocks of one buffer, as the reference's merged q/k/v
+        else:
+            w.grad.add_(part)
+        row += w.size(0)
+
+
+class _Float8Matmul(torch.autograd.Function):
+    """One Linear under MX: y = x . w^T, dX = dY . w, dW = dY^T . x, every operand E4M3 with per-32 scales
+    along the contraction (src/nanochat/model/fp8/fp8.cpp:240-260)."""
+
+    @staticmethod
+    def forward(ctx, x, w, cache):
+        xq = quantize_mx(x)
+        wq = quantize_fp8_weight(w, cache)
+        ctx.save_for_backward(xq.data_t, xq.inv_scale_t, wq.data_t, wq.inv_scale_t)
+        ctx.w = w
+        ctx.direct = mx_grad_direct(w)
+        return mx_gemm(xq.data, xq.inv_scale, wq.data, wq.inv_scale, torch.bfloat16)
+
+    @staticmethod
+    def backward(ctx, go):
+        x_t, x_scale_t, w_t, w_scale_t = ctx.saved_tensors
+        gq = quantize_mx(go.contiguous())
+        dx = mx_gemm(gq.data, gq.inv_scale, w_t, w_scale_t, torch.bfloat16)
+        if ctx.direct:
+            mx_grad_weights(gq.data_t, gq.inv_scale_t, x_t, x_scale_t, [ctx.w])
+            return dx, None, None
+        dw = mx_gemm(gq.data_t, gq.inv_scale_t, x_t, x_scale_t, torch.float32)
+        return dx, dw.to(ctx.w.dtype), None
+
+
+def fp8_matmul(input_2d: torch.Tensor, weight: torch.Tensor, cache: Optional[Fp8WeightCache] = None) -> torch.Tensor:
+    """input_2d (N, in) bf16, weight (out, in) -> (N, out) bf16 under the MX recipe
+    (src/nanochat/model/fp8/fp8.h:40-44, fp8.cpp:566-571). Dims must be % 128: the reference falls back to its
+    tensorwise recipe otherwise, which is outside this library."""
+    if not (mx_fits(input_2d.size(0), input_2d.size(1)) and mx_fits(weight.size(0), weight.size(1))):
+        raise RuntimeError("fp8_matmul: MX needs N, in, out % 128")
+    return _Float8Matmul.apply(input_2d.contiguous(), weight, cache)

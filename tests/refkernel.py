@@ -1,0 +1,49 @@
+"""ctypes door to the reference's own CUDA quantizer (oracle/_ref/libnanochat_ref_quant.so), built by
+oracle/Makefile from the unmodified reference source. A checker for GPU tests; absent when the reference
+tree was not available at build time."""
+from __future__ import annotations
+
+import ctypes
+import os
+
+import torch
+
+_PATH = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "oracle", "_ref",
+                     "libnanochat_ref_quant.so")
+_lib = None
+
+
+def available() -> bool:
+    return os.path.exists(_PATH)
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        _lib = ctypes.CDLL(_PATH)
+        vp, i64, i32 = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int
+        _lib.ref_quantize_mx.argtypes = [vp, i32, i64, i64, vp, i64, vp, i64, vp, i64, vp, i64, i32, vp]
+        _lib.ref_quantize_mx_relu_square_bwd.argtypes = [vp, vp, i64, i64, vp, i64, vp, i64, vp, i64, vp, i64, vp]
+    return _lib
+
+
+def quantize_mx(x: torch.Tensor, relu_square: bool = False, h: torch.Tensor | None = None):
+    """Runs nanochat::kernels::quantize_mx (or the relu^2 backward variant when h is given) on the GPU and
+    returns (data, scale, data_t, scale_t) uint8 tensors."""
+    R, C = x.shape
+    dev = x.device
+    data = torch.zeros((R, C), dtype=torch.uint8, device=dev)
+    data_t = torch.zeros((C, R), dtype=torch.uint8, device=dev)
+    scale = torch.zeros(R * C // 32, dtype=torch.uint8, device=dev)
+    scale_t = torch.zeros(R * C // 32, dtype=torch.uint8, device=dev)
+    stream = torch.cuda.current_stream().cuda_stream
+    if h is None:
+        err = lib().ref_quantize_mx(x.data_ptr(), int(x.dtype == torch.bfloat16), R, C, data.data_ptr(), C,
+                                    scale.data_ptr(), C // 128, data_t.data_ptr(), R, scale_t.data_ptr(), R // 128,
+                                    int(relu_square), stream)
+    else:
+        err = lib().ref_quantize_mx_relu_square_bwd(x.data_ptr(), h.data_ptr(), R, C, data.data_ptr(), C,
+                                                    scale.data_ptr(), C // 128, data_t.data_ptr(), R,
+                                                    scale_t.data_ptr(), R // 128, stream)
+    assert err == 0, f"reference kernel launch failed: cudaError {err}"
+    return data, scale, data_t, scale_t

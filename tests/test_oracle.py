@@ -1,0 +1,150 @@
+"""CPU: the numpy oracle against the reference's torch-op formulation, the plain-C oracle, and the golden
+bytes written by the reference's own CUDA kernel (tests/golden)."""
+import ctypes
+import glob
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import quantizer_input, gemm_operands, np_f32, np_u8
+from oracle import mx_oracle as mo
+from oracle import torch_reference as tr
+
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+SHAPES = [(128, 128), (256, 384), (384, 1024)]  # tests/test_fp8.cpp:158
+
+
+@pytest.mark.parametrize("rows,cols", SHAPES)
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("relu_square", [False, True])
+def test_numpy_oracle_matches_reference_torch_ops(rows, cols, dtype, relu_square):
+    """Mirrors Fp8.MxQuantizeMatchesTorchOps (tests/test_fp8.cpp:156-181) with the oracle in the kernel's seat."""
+    if relu_square and dtype != torch.bfloat16:
+        pytest.skip("relu^2 reads bf16 only")
+    x = quantizer_input(rows, cols).to(dtype)
+    want = tr.quantize_mx(x, True, True, relu_square)
+    got = mo.quantize_mx(np_f32(x), True, True, mo.PROLOGUE_RELU_SQUARE if relu_square else mo.PROLOGUE_NONE)
+    for key in ("data", "scale", "data_t", "scale_t"):
+        assert np.array_equal(np_u8(want[key]).reshape(-1), got[key].reshape(-1)), key
+
+
+def test_e4m3_cast_matches_torch_over_the_whole_range():
+    v = torch.linspace(-448, 448, 400001)
+    assert np.array_equal(np_u8(v.to(torch.float8_e4m3fn)), mo.e4m3_from_f32(v.numpy()))
+    g = torch.Generator().manual_seed(1)
+    v = (torch.randn(200000, generator=g) * torch.logspace(-12, 2, 200000)).clamp(-448, 448)
+    assert np.array_equal(np_u8(v.to(torch.float8_e4m3fn)), mo.e4m3_from_f32(v.numpy()))
+    # every byte round-trips
+    b = np.arange(256, dtype=np.uint8)
+    vals = mo.e4m3_to_f32(b)
+    ok = ~np.isnan(vals)
+    back = mo.e4m3_from_f32(vals[ok])
+    assert np.array_equal(back & 0x7F, b[ok] & 0x7F)
+
+
+def test_saturation_nan_inf():
+    x = np.array([500.0, -1e9, np.inf, -np.inf, np.nan, 464.0, 463.9, 448.0], dtype=np.float32)
+    assert mo.e4m3_from_f32(x).tolist() == [0x7E, 0xFE, 0x7E, 0xFE, 0x7F, 0x7E, 0x7E, 0x7E]
+
+
+def test_scale_rules_differ_only_above_mantissa_1_75():
+    amax = np.array([1.8 * 512, 448.0, 1.0, 1.76, 1.75, 0.0, 1.5 * 2.0 ** 127, 1e-45], dtype=np.float32)
+    ref, flo = mo.mx_exponent(amax, 0), mo.mx_exponent(amax, 1)
+    assert (ref - flo).tolist() == [1, 0, 0, 1, 0, 0, 0, 0]
+    assert ref[5] == 0 and ref[6] <= 253
+    # reference rule never needs saturation: amax * 2^(127 - e) <= 448
+    big = np.abs(np.random.default_rng(0).standard_normal(10000).astype(np.float32)) * 1e3 + 1e-3
+    assert np.all(big * mo.mx_multiplier(mo.mx_exponent(big, 0)) <= 448.0)
+    assert np.any(big * mo.mx_multiplier(mo.mx_exponent(big, 1)) > 448.0)
+
+
+def test_swizzle_is_the_index_function():
+    R, B = 256, 12
+    e = np.arange(R * B, dtype=np.uint32).reshape(R, B)
+    s = mo.swizzle((e % 251).astype(np.uint8))
+    for r, b in [(0, 0), (1, 0), (31, 3), (32, 0), (127, 11), (128, 4), (255, 11)]:
+        assert s[mo.mx_scale_index(r, b, B // 4)] == e[r, b] % 251
+    assert np.array_equal(mo.unswizzle(s, R, B), (e % 251).astype(np.uint8))
+
+
+@pytest.mark.parametrize("rule", [0, 1])
+@pytest.mark.parametrize("prologue", [0, 1, 2])
+def test_c_oracle_matches_numpy_oracle(oracle_c, rule, prologue):
+    R, C = 256, 384
+    x = np_f32(quantizer_input(R, C, seed=3).to(torch.bfloat16))
+    x[5, 7], x[6, 70], x[7, 100] = np.nan, np.inf, -np.inf
+    h = np_f32(torch.randn(R, C, generator=torch.Generator().manual_seed(4)).to(torch.bfloat16))
+    want = mo.quantize_mx(x, True, True, prologue, h, rule)
+    vp, i64 = ctypes.c_void_p, ctypes.c_int64
+    for transposed in (0, 1):
+        Rr, Cc = (C, R) if transposed else (R, C)
+        data = np.zeros((Rr, Cc), np.uint8)
+        scale = np.zeros(Rr * Cc // 32, np.uint8)
+        oracle_c.mxo_quantize(x.ctypes.data_as(vp), h.ctypes.data_as(vp), i64(R), i64(C), transposed, prologue, rule,
+                              data.ctypes.data_as(vp), i64(Cc), scale.ctypes.data_as(vp), i64(Cc // 128))
+        assert np.array_equal(data, want["data_t" if transposed else "data"])
+        assert np.array_equal(scale, want["scale_t" if transposed else "scale"])
+
+
+def test_gemm_oracles_agree(oracle_c):
+    """numpy dequantize -> fp32 matmul vs the C oracle's double-precision triple loop, and both vs the
+    reference's torch-op dequantize (tests/test_fp8.cpp:43-49, 206)."""
+    M, N, K = 128, 256, 384
+    a, b = gemm_operands(M, N, K)
+    qa, qb = mo.quantize_mx(np_f32(a), True, False), mo.quantize_mx(np_f32(b), True, False)
+    ref = mo.mx_gemm_ref(qa["data"], qa["scale"], qb["data"], qb["scale"])
+    d = np.zeros((M, N), np.float32)
+    vp, i64 = ctypes.c_void_p, ctypes.c_int64
+    oracle_c.mxo_gemm_f32(qa["data"].ctypes.data_as(vp), qa["scale"].ctypes.data_as(vp), qb["data"].ctypes.data_as(vp),
+                          qb["scale"].ctypes.data_as(vp), d.ctypes.data_as(vp), i64(M), i64(N), i64(K),
+                          ctypes.c_float(1.0), 0)
+    assert mo.rel_norm_diff(ref, d) < 1e-6
+    ta = tr.mx_dequantize(torch.from_numpy(qa["data"]).view(torch.float8_e4m3fn), torch.from_numpy(qa["scale"]))
+    tb = tr.mx_dequantize(torch.from_numpy(qb["data"]).view(torch.float8_e4m3fn), torch.from_numpy(qb["scale"]))
+    assert mo.rel_norm_diff(ref, torch.mm(ta, tb.t()).numpy()) < 1e-6
+
+
+def test_residual_rounding_is_two_roundings(oracle_c):
+    acc = np.array([1.00390625, 3.0000001, -2.5], dtype=np.float32)
+    r = np.array([1.0, 1e-3, 2.5], dtype=np.float32)
+    out = mo.gemm_bf16_out(acc, r)
+    want = mo.round_bf16(mo.round_bf16(acc) + r)
+    assert np.array_equal(out, want)
+    for i in range(3):
+        assert oracle_c.mxo_bf16_out(float(acc[i]), 1, float(r[i])) == out[i]
+
+
+def _golden_files():
+    return sorted(glob.glob(os.path.join(GOLDEN, "quantize_*.npz")))
+
+
+@pytest.mark.parametrize("path", _golden_files() or [None])
+def test_oracle_matches_reference_kernel_golden(path):
+    """Bytes the reference's own nanochat_mx_quantize_* kernels wrote on a B200 (tests/golden/make_golden.py)."""
+    if path is None:
+        pytest.skip("no golden files yet")
+    g = np.load(path)
+    x = mo.bf16_bits_to_f32(g["x_bf16_bits"]) if "x_bf16_bits" in g else g["x_f32"]
+    pro = int(g["prologue"])
+    h = mo.bf16_bits_to_f32(g["h_bf16_bits"]) if "h_bf16_bits" in g else None
+    want = mo.quantize_mx(x, True, True, pro, h)
+    for key in ("data", "scale", "data_t", "scale_t"):
+        assert np.array_equal(want[key].reshape(-1), g[key].reshape(-1)), (os.path.basename(path), key)
+
+
+def _gemm_golden_files():
+    return sorted(glob.glob(os.path.join(GOLDEN, "gemm_*.npz")))
+
+
+@pytest.mark.parametrize("path", _gemm_golden_files() or [None])
+def test_gemm_oracle_matches_cublaslt_golden(path):
+    """fp32 outputs of cuBLASLt's MXFP8 GEMM (the reference's --gemm=cublas arithmetic, mx_gemm.cpp:158) on a
+    B200 for the same quantized operands. Tolerance 1e-5, the reference's own backend-vs-backend bar for fp32
+    (tests/test_fp8.cpp:343)."""
+    if path is None:
+        pytest.skip("no golden files yet")
+    g = np.load(path)
+    ref = mo.mx_gemm_ref(g["a"], g["a_scale"], g["b"], g["b_scale"])
+    assert mo.rel_norm_diff(ref, g["d_f32"]) < 1e-5

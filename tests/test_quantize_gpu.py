@@ -1,0 +1,146 @@
+"""GPU parity of the MX quantizer, through the C ABI: bit-exact against the CPU oracle and against the
+reference's own CUDA kernel compiled from its source."""
+import numpy as np
+import pytest
+import torch
+
+import nanochat_cpp_b200 as nc
+import refkernel
+from helpers import assert_quantized_equal, np_u8, oracle_quantize, quantizer_input
+from oracle import mx_oracle as mo
+
+pytestmark = pytest.mark.gpu
+SHAPES = [(128, 128), (256, 384), (384, 1024)]  # tests/test_fp8.cpp:158
+
+
+@pytest.mark.parametrize("rows,cols", SHAPES)
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("relu_square", [False, True])
+def test_matches_oracle(rows, cols, dtype, relu_square):
+    """Fp8.MxQuantizeMatchesTorchOps (tests/test_fp8.cpp:156-181): bytes and swizzled scales, both layouts."""
+    if relu_square and dtype != torch.bfloat16:
+        pytest.skip("relu^2 reads bf16 only")
+    x = quantizer_input(rows, cols).to(dtype)
+    q = nc.quantize_mx(x.cuda(), True, True, relu_square)
+    want = oracle_quantize(x, True, True, mo.PROLOGUE_RELU_SQUARE if relu_square else 0)
+    assert_quantized_equal(q, want, f"{rows}x{cols} {dtype} relu2={relu_square}")
+
+
+@pytest.mark.parametrize("rule", [nc.SCALE_REFERENCE, nc.SCALE_OCP_FLOOR])
+def test_scale_rules(rule):
+    x = quantizer_input(256, 384, seed=5).to(torch.bfloat16)
+    q = nc.quantize_mx(x.cuda(), scale_rule=rule)
+    assert_quantized_equal(q, oracle_quantize(x, rule=rule), f"rule {rule}")
+
+
+def test_rows_only_and_cols_only():
+    x = quantizer_input(256, 256, seed=2).to(torch.bfloat16)
+    want = oracle_quantize(x)
+    q = nc.quantize_mx(x.cuda(), True, False)
+    assert q.data_t is None
+    assert_quantized_equal(q, {k: want[k] for k in ("data", "scale")}, "rows only")
+    q = nc.quantize_mx(x.cuda(), False, True)
+    assert q.data is None
+    assert_quantized_equal(q, {k: want[k] for k in ("data_t", "scale_t")}, "cols only")
+
+
+def test_nan_inf_zero_and_extremes():
+    """amax skips NaN, elements saturate, the exponent clamps (mx_kernel.cuh:29-34, 61, 82-90)."""
+    x = quantizer_input(128, 256, seed=7)
+    x[3, 5] = float("nan")
+    x[4, 64:96] = float("nan")  # a block of only NaN
+    x[5, 100] = float("inf")
+    x[6, 130] = float("-inf")
+    x[7, :] = 0
+    x[8, 0:32] = 3e38
+    x[9, 32:64] = 1e-45
+    x[10, 64:96] = -0.0
+    for dtype in (torch.float32, torch.bfloat16):
+        xd = x.to(dtype)
+        q = nc.quantize_mx(xd.cuda())
+        assert_quantized_equal(q, oracle_quantize(xd), f"edge cases {dtype}")
+
+
+def test_relu_square_bwd():
+    g = torch.Generator().manual_seed(11)
+    gr = (torch.randn(256, 384, generator=g) * torch.logspace(-3, 1, 384)).to(torch.bfloat16)
+    h = torch.randn(256, 384, generator=g).to(torch.bfloat16)
+    q = nc.quantize_mx_relu_square_bwd(gr.cuda(), h.cuda())
+    assert_quantized_equal(q, oracle_quantize(gr, prologue=mo.PROLOGUE_RELU_SQUARE_BWD, h=h), "relu^2 bwd")
+
+
+def test_subview_merged_qkv():
+    """Three weights quantized into row ranges of one buffer and column ranges of its transpose
+    (fp8.cpp:155-171); equals quantizing the concatenation."""
+    g = torch.Generator().manual_seed(13)
+    ws = [torch.randn(r, 256, generator=g) * 0.05 for r in (128, 256, 128)]
+    out = nc.mx_qkv_weights(*[w.cuda() for w in ws])
+    want = oracle_quantize(torch.cat(ws, 0))
+    got = nc.Fp8Tensor(out[0], out[1], out[2], out[3])
+    assert_quantized_equal(got, want, "merged qkv")
+
+
+def test_shape_and_alignment_errors():
+    x = torch.zeros(128, 96, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(RuntimeError):
+        nc.quantize_mx(x)
+    x = torch.zeros(128, 128, dtype=torch.float32, device="cuda")
+    with pytest.raises(RuntimeError):
+        nc.quantize_mx(x, relu_square=True)
+    # 16-byte but not 32-byte aligned buffers take the narrow load/store path
+    base = torch.zeros(256 * 256 + 8, dtype=torch.float32, device="cuda")
+    xin = quantizer_input(256, 256, seed=17)
+    view = base[4:4 + 256 * 256].view(256, 256)
+    assert view.data_ptr() % 32 == 16
+    view.copy_(xin)
+    assert_quantized_equal(nc.quantize_mx(view), oracle_quantize(xin), "16-byte aligned fp32 input")
+
+
+@pytest.mark.skipif(not refkernel.available(), reason="reference kernel library not built")
+@pytest.mark.parametrize("rows,cols,dtype", [(256, 384, torch.bfloat16), (384, 1024, torch.float32),
+                                             (16384, 1536, torch.bfloat16), (2048, 6144, torch.bfloat16)])
+def test_matches_reference_cuda_kernel(rows, cols, dtype):
+    """Same input through nanochat_mx_quantize_* (the reference's kernel, unmodified) and through this library:
+    identical bytes, at BASELINE sizes too."""
+    g = torch.Generator(device="cuda").manual_seed(0)
+    x = (torch.randn(rows, cols, generator=g, device="cuda") * torch.logspace(-4, 4, cols, device="cuda")).to(dtype)
+    for relu_square in (False, True):
+        if relu_square and dtype != torch.bfloat16:
+            continue
+        ref = refkernel.quantize_mx(x, relu_square)
+        q = nc.quantize_mx(x, True, True, relu_square)
+        for got, want, name in zip((q.data, q.inv_scale, q.data_t, q.inv_scale_t), ref, ("data", "scale", "data_t", "scale_t")):
+            assert torch.equal(got.view(torch.uint8).reshape(-1), want.reshape(-1)), f"{name} relu2={relu_square}"
+
+
+@pytest.mark.skipif(not refkernel.available(), reason="reference kernel library not built")
+def test_oracle_matches_reference_cuda_kernel():
+    """Pins the oracle itself against the reference's kernel run here."""
+    x = quantizer_input(256, 384, seed=21).to(torch.bfloat16)
+    ref = refkernel.quantize_mx(x.cuda())
+    want = oracle_quantize(x)
+    for t, key in zip(ref, ("data", "scale", "data_t", "scale_t")):
+        assert np.array_equal(t.cpu().numpy().reshape(-1), want[key].reshape(-1)), key
+
+
+def test_full_size_roundtrip_property():
+    """Config 2's activation shape: dequantized values lie within half an E4M3 ulp of the input and every
+    scale is the smallest admissible power of two (size-independent properties, checked on the GPU)."""
+    g = torch.Generator(device="cuda").manual_seed(3)
+    x = torch.randn(16384, 1536, generator=g, device="cuda").to(torch.bfloat16)
+    q = nc.quantize_mx(x)
+    e = q.inv_scale.view(torch.uint8).view(128, 12, 32, 4, 4).permute(0, 3, 2, 1, 4).reshape(16384, 48).float()
+    scale = torch.exp2(e - 127)
+    deq = q.data.float().view(16384, 48, 32) * scale.unsqueeze(-1)
+    xb = x.float().view(16384, 48, 32)
+    amax = xb.abs().amax(-1)
+    assert torch.all(amax / scale <= 448)
+    assert torch.all(amax / scale > 224)          # one exponent lower would overflow
+    # relative error of normal values: at most 2^-4 (3 mantissa bits, round to nearest)
+    big = xb.abs() >= (scale * 2.0 ** -6).unsqueeze(-1)
+    rel = ((deq - xb).abs() / xb.abs().clamp_min(1e-30))[big]
+    assert rel.max().item() <= 2.0 ** -4 + 1e-6
+    # the transposed layout holds the same tensor: dequantize and compare loosely
+    et = q.inv_scale_t.view(torch.uint8).view(12, 128, 32, 4, 4).permute(0, 3, 2, 1, 4).reshape(1536, 512).float()
+    deqt = (q.data_t.float().view(1536, 512, 32) * torch.exp2(et - 127).unsqueeze(-1)).view(1536, 16384)
+    assert (deqt.t() - x.float()).norm() / x.float().norm() < 0.04
