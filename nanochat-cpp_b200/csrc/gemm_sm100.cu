@@ -6,7 +6,7 @@
 // Structure (one CTA per SM, persistent over output tiles, 192 threads):
 //   warp 0      producer: TMA loads of a 128 x 128-byte A tile and a BN x 128-byte B tile (128-byte swizzle)
 //               plus untiled bulk copies of the 512-byte scale tiles, into a ring of shared-memory stages
-//               guarded by full/empty mbarriers. No cluster multicast anywhere.
+//               guarded by full/empty mbarriers. Every load lands in the CTA that issued it.
 //   warp 1      MMA issuer (one thread): per stage, tcgen05.cp moves the scale tiles into TMEM (4 columns per
 //               128 rows, byte = K block), then four tcgen05.mma kind::mxf8f6f4.block_scale steps of K = 32;
 //               tcgen05.commit releases the stage and, after the last K step, publishes the accumulator.
@@ -639,17 +639,20 @@ extern "C" int mxb200_gemm_splits(int64_t M, int64_t N, int64_t K) {
   const int bn = mxb200::choose_bn(N);
   const int64_t tiles = (M / 128) * ((N + bn - 1) / bn);
   const int64_t k_tiles = K / 128;
-  // split only while a single wave leaves SMs idle and every slice keeps a deep main loop
+  // Splitting costs a round trip of fp32 partial tiles through the workspace, so it only pays when the tiles
+  // alone cannot fill the machine for two waves and every slice keeps a deep main loop.
+  if (tiles >= 2 * dev.sms)
+    return 1;
   int best = 1;
-  double best_eff = 0.0;
-  for (int s = 1; s <= 8; ++s) {
-    if (k_tiles / s < 16 && s > 1)
+  double best_score = 0.0;
+  for (int s = 1; s <= 4; ++s) {
+    if (s > 1 && k_tiles / s < 32)
       break;
     const int64_t units = tiles * s;
     const int64_t waves = (units + dev.sms - 1) / dev.sms;
-    const double eff = static_cast<double>(units) / static_cast<double>(waves * dev.sms) * (s == 1 ? 1.0 : 0.97);
-    if (eff > best_eff + 0.02) {
-      best_eff = eff;
+    const double score = static_cast<double>(units) / static_cast<double>(waves * dev.sms) * (s == 1 ? 1.0 : 0.9);
+    if (score > best_score + 1e-9) {
+      best_score = score;
       best = s;
     }
   }

@@ -1,6 +1,7 @@
-// Inline-PTX wrappers for the sm_100a features the GEMM uses: mbarrier, TMA (cp.async.bulk[.tensor], never
-// with cluster multicast), tensor memory (tcgen05.alloc/ld/cp) and the 5th-generation tensor-core MMA
-// (tcgen05.mma kind::mxf8f6f4.block_scale). Device-only.
+// Inline-PTX wrappers for the sm_100a features the GEMM uses: mbarrier, TMA loads (every load lands in the
+// shared memory of the CTA that issued it), tensor memory (tcgen05.alloc/ld/cp), the 5th-generation
+// tensor-core MMA (tcgen05.mma kind::mxf8f6f4.block_scale) in its one-CTA and CTA-pair forms, and the
+// cluster plumbing a CTA pair needs (rank, remote mbarrier arrive, cluster barrier). Device-only.
 #pragma once
 
 #include <cstdint>
@@ -196,6 +197,91 @@ __host__ __device__ constexpr uint32_t make_idesc_mxf8(uint32_t m, uint32_t n) {
 
 __device__ __forceinline__ uint32_t idesc_with_sf(uint32_t idesc, uint32_t a_sf_id, uint32_t b_sf_id) {
   return idesc | (b_sf_id << 4) | (a_sf_id << 29);
+}
+
+// ---------------------------------------------------------------------------------------------- CTA pairs
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+
+// The shared::cluster address of the same shared-memory offset in the CTA of the given rank.
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+
+__device__ __forceinline__ void cluster_arrive() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void cluster_wait() {
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// Arrive on an mbarrier anywhere in the cluster (address from map_to_cta).
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+
+// Tiled loads for a CTA pair: data lands in the issuing CTA's shared memory, the byte count is credited to an
+// mbarrier that may live in the pair's other CTA (cluster address).
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* map, uint32_t bar_cluster_addr,
+                                                 int32_t x, int32_t y) {
+  asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster_addr), "r"(x), "r"(y)
+        : "memory");
+}
+
+__device__ __forceinline__ void tma_load_4d_pair(void* smem_dst, const CUtensorMap* map, uint32_t bar_cluster_addr,
+                                                 int32_t c0, int32_t c1, int32_t c2, int32_t c3) {
+  asm volatile(
+        "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster_addr), "r"(c0), "r"(c1),
+        "r"(c2), "r"(c3)
+        : "memory");
+}
+
+// Tensor memory of both CTAs of a pair: the same warp of each CTA executes these.
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_out, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_out)), "r"(cols)
+               : "memory");
+}
+
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+
+// Completion of the pair's MMAs / copies so far arrives on the mbarrier at this offset in every CTA of cta_mask.
+__device__ __forceinline__ void tcgen05_commit_pair(uint64_t* bar, uint16_t cta_mask) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(smem_u32(bar)), "h"(cta_mask)
+               : "memory");
+}
+
+// Each CTA of the pair copies the scale tile at this offset of its own shared memory into its own TMEM.
+__device__ __forceinline__ void tcgen05_cp_32x128b_warpx4_pair(uint32_t taddr, uint64_t smem_desc) {
+  asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(smem_desc) : "memory");
+}
+
+// One K = 32 step of a 256-row MMA across the pair: each CTA supplies 128 rows of A and half of B's rows from
+// the same shared-memory offsets and accumulates its 128 rows of D in its own TMEM.
+__device__ __forceinline__ void tcgen05_mma_mxf8_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                                      uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
+  asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}\n"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
+        : "memory");
 }
 
 }  // namespace mxb200

@@ -1,0 +1,273 @@
+"""The data-parallel GEMM workload of one nanochat training step, on one rank.
+
+Every Linear of a depth-`n_layer` nanochat model (merged QKV, attention out, MLP fc, MLP proj; then the
+chunked lm_head) runs forward, dgrad and wgrad through the MXFP8 engine on this rank's own micro-batch, the
+weight gradients leave as bf16 straight into one contiguous bucket, and each layer's slice of the bucket is
+reduce-scattered (average) across ranks while the next layer's backward runs. Nothing else of the model runs:
+attention, norms and the loss are outside this path, so their outputs are seeded synthetic tensors of the
+right shape and distribution.
+
+Call sites mirrored (paths within nanochat-cpp): the per-Linear sequence of src/nanochat/model/fp8/fp8.cpp:
+240-260 (Float8Matmul), 424-462 (MxQkv), 265-338 (Fp8ReluSquareMlp, MX branch), the chunked lm_head of
+src/nanochat/model/ops/softcap_ce.cpp:27-110, and the gradient reduce-scatter of
+src/nanochat/train/optim.cpp:425-431, 459-468.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Callable, List, Optional
+
+import torch
+import torch.distributed as dist
+
+from . import engine as nc
+
+
+@dataclass
+class StepConfig:
+    """Shapes of config_from_depth (src/nanochat/model/gpt.cpp:25-39): n_embd = 64 * depth."""
+    n_layer: int = 24
+    n_embd: int = 1536
+    vocab: int = 32768
+    tokens: int = 16384          # per rank: batch 8 x sequence 2048
+    chunk_rows: int = 2048       # lm_head row chunk
+
+    @property
+    def linear_shapes(self):
+        C = self.n_embd
+        return [("qkv", 3 * C, C), ("attn_out", C, C), ("mlp_fc", 4 * C, C), ("mlp_proj", C, 4 * C)]
+
+    @property
+    def layer_params(self) -> int:
+        return sum(n * k for _, n, k in self.linear_shapes)
+
+    @property
+    def lm_head_params(self) -> int:
+        return self.vocab * self.n_embd
+
+    def flops_per_step(self) -> float:
+        """2MNK over every GEMM: forward, dgrad and wgrad of each Linear."""
+        layer = sum(3 * 2.0 * self.tokens * n * k for _, n, k in self.linear_shapes)
+        return self.n_layer * layer + 3 * 2.0 * self.tokens * self.vocab * self.n_embd
+
+
+class GradBucket:
+    """One contiguous bf16 buffer holding every weight gradient in backward order of use: segment i is layer i's
+    four matrices (qkv, attn_out, mlp_fc, mlp_proj), the last segment is lm_head. wgrad GEMMs write their bf16
+    output directly at these offsets, so no cast pass precedes the collective (the reference casts a stacked
+    fp32 buffer first, src/nanochat/train/optim.cpp:459). Each segment is reduce-scattered on its own: rank r
+    keeps elements [r * len / world, (r + 1) * len / world) of the segment, averaged over ranks."""
+
+    def __init__(self, cfg: StepConfig, device, world: int = 1):
+        self.cfg, self.world = cfg, world
+        self.segments: List[tuple] = []  # (offset, length)
+        off = 0
+        for _ in range(cfg.n_layer):
+            self.segments.append((off, cfg.layer_params))
+            off += cfg.layer_params
+        self.segments.append((off, cfg.lm_head_params))
+        off += cfg.lm_head_params
+        for _, length in self.segments:
+            if length % world:
+                raise ValueError("every bucket segment must divide evenly across ranks")
+        self.numel = off
+        self.buffer = torch.empty(off, dtype=torch.bfloat16, device=device)
+        self.shards = [torch.empty(length // world, dtype=torch.bfloat16, device=device) for _, length in self.segments]
+
+    def matrix(self, layer: int, index: int) -> torch.Tensor:
+        """The (out, in) gradient matrix `index` of `layer` as a view of the bucket."""
+        off = self.segments[layer][0]
+        for j, (_, n, k) in enumerate(self.cfg.linear_shapes):
+            if j == index:
+                return self.buffer[off:off + n * k].view(n, k)
+            off += n * k
+        raise IndexError(index)
+
+    def lm_head(self) -> torch.Tensor:
+        off, length = self.segments[-1]
+        return self.buffer[off:off + length].view(self.cfg.vocab, self.cfg.n_embd)
+
+    def segment(self, i: int) -> torch.Tensor:
+        off, length = self.segments[i]
+        return self.buffer[off:off + length]
+
+    def reduce_scatter(self, i: int, group=None, async_op: bool = False):
+        """Average segment i across ranks into this rank's shard. world == 1: a copy."""
+        if self.world == 1 or not dist.is_initialized():
+            self.shards[i].copy_(self.segment(i))
+            return None
+        return dist.reduce_scatter_tensor(self.shards[i], self.segment(i), op=dist.ReduceOp.AVG, group=group,
+                                          async_op=async_op)
+
+
+def _student_t(shape, nu: float, gen, device) -> torch.Tensor:
+    """N(0,1) / sqrt(chi2_nu / nu) from the seeded generator."""
+    z = torch.randn(shape, generator=gen, device=device)
+    chi2 = torch.zeros(shape, device=device)
+    for _ in range(int(nu)):
+        chi2 += torch.randn(shape, generator=gen, device=device) ** 2
+    return z / torch.sqrt(chi2 / nu)
+
+
+class DpStep:
+    """Buffers and launch sequence of one rank's step. `gemm_hook(begin: bool)` (optional) is called right before
+    and right after every GEMM launch so a benchmark can bracket them with events."""
+
+    def __init__(self, cfg: StepConfig, device, rank: int = 0, world: int = 1, input_sets: int = 2,
+                 gemm_hook: Optional[Callable[[bool], None]] = None):
+        self.cfg, self.device, self.rank, self.world = cfg, device, rank, world
+        self.hook = gemm_hook
+        M, C, V = cfg.tokens, cfg.n_embd, cfg.vocab
+        gen = torch.Generator(device=device).manual_seed(1000 + rank)
+        bf = torch.bfloat16
+
+        def randn(shape, std=1.0):
+            return (torch.randn(shape, generator=gen, device=device) * std).to(bf)
+
+        # fp32 master weights, one set per layer, ~N(0, 1/sqrt(K)); identical on every rank (seed without rank)
+        wgen = torch.Generator(device=device).manual_seed(7)
+        self.weights = [[torch.randn((n, k), generator=wgen, device=device) / k ** 0.5 for _, n, k in cfg.linear_shapes]
+                        for _ in range(cfg.n_layer)]
+        self.w_lm = torch.randn((V, C), generator=wgen, device=device) / C ** 0.5
+        self.wq: List[List[nc.Fp8Tensor]] = [[nc.empty_mx(n, k, device) for _, n, k in cfg.linear_shapes]
+                                             for _ in range(cfg.n_layer)]
+        self.wq_lm = nc.empty_mx(V, C, device)
+
+        # synthetic activations / incoming gradients, a few sets used in rotation
+        self.x_attn = [randn((M, C)) for _ in range(input_sets)]
+        self.y_att = [randn((M, C)) for _ in range(input_sets)]
+        self.x_mlp = [randn((M, C)) for _ in range(input_sets)]
+        self.resid = [randn((M, C)) for _ in range(input_sets)]
+        self.dy_proj = [randn((M, C), 1e-3) for _ in range(input_sets)]
+        self.dy_o = [randn((M, C), 1e-3) for _ in range(input_sets)]
+        self.dy_qkv = [randn((M, 3 * C), 1e-3) for _ in range(input_sets)]
+        self.x_lm = (0.5 * _student_t((M, C), 3.0, gen, device)).to(bf)
+        self.dlogits = [randn((cfg.chunk_rows, V), 1e-3) for _ in range(input_sets)]
+
+        # saved for backward, per layer: the transposed (column-wise) quantizations and the MLP hidden
+        L = cfg.n_layer
+        self.xq_attn = [nc.empty_mx(M, C, device) for _ in range(L)]
+        self.yq_att = [nc.empty_mx(M, C, device) for _ in range(L)]
+        self.xq_mlp = [nc.empty_mx(M, C, device) for _ in range(L)]
+        self.aq = [nc.empty_mx(M, 4 * C, device) for _ in range(L)]
+        self.h = [torch.empty((M, 4 * C), dtype=bf, device=device) for _ in range(L)]
+        # outputs and scratch shared by all layers
+        self.qkv = torch.empty((M, 3 * C), dtype=bf, device=device)
+        self.out_c = torch.empty((M, C), dtype=bf, device=device)
+        self.gq_c = nc.empty_mx(M, C, device)
+        self.gq_3c = nc.empty_mx(M, 3 * C, device)
+        self.gq_4c = nc.empty_mx(M, 4 * C, device)
+        self.da = torch.empty((M, 4 * C), dtype=bf, device=device)
+        self.dx = torch.empty((M, C), dtype=bf, device=device)
+        # lm_head
+        self.xq_lm = nc.empty_mx(M, C, device)
+        self.logits = torch.empty((cfg.chunk_rows, V), dtype=bf, device=device)
+        self.gq_lm = nc.empty_mx(M, V, device)
+        self.dx_lm = torch.empty((M, C), dtype=bf, device=device)
+
+        self.bucket = GradBucket(cfg, device, world)
+        self.comm_stream = torch.cuda.Stream(device=device) if device.type == "cuda" else None
+        self._pending: list = []
+
+    # ------------------------------------------------------------------ pieces
+    def _gemm(self, out, a, a_scale, b, b_scale, resid=None):
+        if self.hook:
+            self.hook(True)
+        nc.mx_gemm_out(out, a, a_scale, b, b_scale, resid)
+        if self.hook:
+            self.hook(False)
+
+    def _quant(self, x, q: nc.Fp8Tensor, relu_square=False):
+        out, out_t = nc.mx_outs(q)
+        nc.quantize_mx_into(x, relu_square, out, out_t)
+
+    def quantize_weights(self):
+        """Once per optimizer step (the reference's weight cache, fp8.cpp:516-536): fp32 masters -> both layouts."""
+        for ws, qs in zip(self.weights, self.wq):
+            for w, q in zip(ws, qs):
+                self._quant(w, q)
+        self._quant(self.w_lm, self.wq_lm)
+
+    def layer_forward(self, l: int, s: int):
+        wq = self.wq[l]
+        self._quant(self.x_attn[s], self.xq_attn[l])
+        self._gemm(self.qkv, self.xq_attn[l].data, self.xq_attn[l].inv_scale, wq[0].data, wq[0].inv_scale)
+        self._quant(self.y_att[s], self.yq_att[l])
+        self._gemm(self.out_c, self.yq_att[l].data, self.yq_att[l].inv_scale, wq[1].data, wq[1].inv_scale, self.resid[s])
+        self._quant(self.x_mlp[s], self.xq_mlp[l])
+        self._gemm(self.h[l], self.xq_mlp[l].data, self.xq_mlp[l].inv_scale, wq[2].data, wq[2].inv_scale)
+        self._quant(self.h[l], self.aq[l], relu_square=True)
+        self._gemm(self.out_c, self.aq[l].data, self.aq[l].inv_scale, wq[3].data, wq[3].inv_scale, self.resid[s])
+
+    def layer_backward(self, l: int, s: int):
+        wq, b = self.wq[l], self.bucket
+        # MLP proj: dA = dY . W, dW = dY^T . A
+        self._quant(self.dy_proj[s], self.gq_c)
+        self._gemm(self.da, self.gq_c.data, self.gq_c.inv_scale, wq[3].data_t, wq[3].inv_scale_t)
+        self._gemm(b.matrix(l, 3), self.gq_c.data_t, self.gq_c.inv_scale_t, self.aq[l].data_t, self.aq[l].inv_scale_t)
+        # relu^2 backward fused into the quantizer: dh = bf16(h > 0 ? dA * 2h : 0)
+        out, out_t = nc.mx_outs(self.gq_4c)
+        nc.check(nc.lib.mxb200_quantize_mx_relu_square_bwd(self.da.data_ptr(), self.h[l].data_ptr(), self.da.size(0),
+                                                           self.da.size(1), out, out_t, nc.SCALE_REFERENCE,
+                                                           torch.cuda.current_stream().cuda_stream), "quantize dh")
+        self._gemm(self.dx, self.gq_4c.data, self.gq_4c.inv_scale, wq[2].data_t, wq[2].inv_scale_t)
+        self._gemm(b.matrix(l, 2), self.gq_4c.data_t, self.gq_4c.inv_scale_t, self.xq_mlp[l].data_t, self.xq_mlp[l].inv_scale_t)
+        # attention out
+        self._quant(self.dy_o[s], self.gq_c)
+        self._gemm(self.dx, self.gq_c.data, self.gq_c.inv_scale, wq[1].data_t, wq[1].inv_scale_t)
+        self._gemm(b.matrix(l, 1), self.gq_c.data_t, self.gq_c.inv_scale_t, self.yq_att[l].data_t, self.yq_att[l].inv_scale_t)
+        # merged QKV
+        self._quant(self.dy_qkv[s], self.gq_3c)
+        self._gemm(self.dx, self.gq_3c.data, self.gq_3c.inv_scale, wq[0].data_t, wq[0].inv_scale_t)
+        self._gemm(b.matrix(l, 0), self.gq_3c.data_t, self.gq_3c.inv_scale_t, self.xq_attn[l].data_t, self.xq_attn[l].inv_scale_t)
+
+    def lm_head(self):
+        """Chunked logits GEMM, gradient quantized per chunk into row/column ranges of one MX buffer, dX per chunk,
+        one wgrad GEMM over all tokens (softcap_ce.cpp:46-109)."""
+        cfg = self.cfg
+        self._quant(self.x_lm, self.xq_lm)
+        K = cfg.n_embd
+        for c, begin in enumerate(range(0, cfg.tokens, cfg.chunk_rows)):
+            rows = cfg.chunk_rows
+            xa = self.xq_lm.data[begin:begin + rows]
+            xs = self.xq_lm.inv_scale[begin * K // 32:(begin + rows) * K // 32]
+            self._gemm(self.logits, xa, xs, self.wq_lm.data, self.wq_lm.inv_scale)
+            g = self.dlogits[c % len(self.dlogits)]
+            nc.quantize_mx_into(g, False, nc.mx_out(self.gq_lm.data, self.gq_lm.inv_scale, begin, 0),
+                                nc.mx_out(self.gq_lm.data_t, self.gq_lm.inv_scale_t, 0, begin))
+            ga = self.gq_lm.data[begin:begin + rows]
+            gs = self.gq_lm.inv_scale[begin * cfg.vocab // 32:(begin + rows) * cfg.vocab // 32]
+            self._gemm(self.dx_lm[begin:begin + rows], ga, gs, self.wq_lm.data_t, self.wq_lm.inv_scale_t)
+        self._gemm(self.bucket.lm_head(), self.gq_lm.data_t, self.gq_lm.inv_scale_t, self.xq_lm.data_t, self.xq_lm.inv_scale_t)
+
+    def _reduce_segment(self, i: int):
+        """Reduce-scatter segment i on the communication stream once the compute stream has produced it."""
+        if self.world == 1:
+            return
+        ev = torch.cuda.Event()
+        ev.record()
+        self.comm_stream.wait_event(ev)
+        with torch.cuda.stream(self.comm_stream):
+            self._pending.append(self.bucket.reduce_scatter(i, async_op=True))
+
+    def finish_collectives(self):
+        for w in self._pending:
+            if w is not None:
+                w.wait()
+        self._pending.clear()
+        if self.comm_stream is not None:
+            torch.cuda.current_stream().wait_stream(self.comm_stream)
+
+    # ------------------------------------------------------------------ the step
+    def run_step(self, step: int = 0):
+        cfg = self.cfg
+        n_sets = len(self.x_attn)
+        self.quantize_weights()
+        for l in range(cfg.n_layer):
+            self.layer_forward(l, (step + l) % n_sets)
+        self.lm_head()
+        self._reduce_segment(cfg.n_layer)
+        for l in reversed(range(cfg.n_layer)):
+            self.layer_backward(l, (step + l) % n_sets)
+            self._reduce_segment(l)
+        self.finish_collectives()

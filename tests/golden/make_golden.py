@@ -1,0 +1,67 @@
+"""Writes the golden fixtures of tests/golden/ on a machine with a B200.
+
+    make -C oracle && python tests/golden/make_golden.py [outdir]
+
+quantize_*.npz: a seeded CPU-drawn input and the bytes the reference's OWN CUDA quantizer
+(nanochat_mx_quantize_* of src/nanochat/model/fp8/fp8_kernel.cu, compiled unmodified by oracle/Makefile into
+oracle/_ref/) wrote for it on the GPU, both layouts. gemm_*.npz: quantized operands and the fp32 result of
+cuBLASLt's MXFP8 GEMM (torch._scaled_mm, the arithmetic of the reference's --gemm=cublas backend,
+src/nanochat/model/fp8/mx_gemm.cpp:158). The CPU test suite checks the oracle against these files.
+"""
+import os
+import sys
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(os.path.dirname(HERE))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "tests"))
+
+import refkernel  # noqa: E402
+from helpers import gemm_operands, quantizer_input  # noqa: E402
+
+
+def bits(t):
+    return t.view(torch.int16).numpy().view(np.uint16)
+
+
+def main():
+    out = sys.argv[1] if len(sys.argv) > 1 else HERE
+    os.makedirs(out, exist_ok=True)
+    assert refkernel.available(), "build oracle/_ref first (make -C oracle)"
+    cases = [("bf16_128x128", 128, 128, torch.bfloat16, 0), ("bf16_256x384", 256, 384, torch.bfloat16, 0),
+             ("relu2_256x384", 256, 384, torch.bfloat16, 1), ("f32_128x256", 128, 256, torch.float32, 0),
+             ("relu2bwd_128x256", 128, 256, torch.bfloat16, 2)]
+    for name, R, C, dtype, pro in cases:
+        x = quantizer_input(R, C, seed=100 + R + C + pro).to(dtype)
+        x[2, 3] = float("nan")
+        x[3, 70] = float("inf")
+        rec = {"prologue": np.int32(pro)}
+        h = None
+        if pro == 2:
+            h = torch.randn(R, C, generator=torch.Generator().manual_seed(5)).to(torch.bfloat16)
+            rec["h_bf16_bits"] = bits(h)
+        if dtype == torch.bfloat16:
+            rec["x_bf16_bits"] = bits(x)
+        else:
+            rec["x_f32"] = x.numpy()
+        data, scale, data_t, scale_t = refkernel.quantize_mx(x.cuda(), pro == 1, None if h is None else h.cuda())
+        torch.cuda.synchronize()
+        rec.update(data=data.cpu().numpy(), scale=scale.cpu().numpy(), data_t=data_t.cpu().numpy(), scale_t=scale_t.cpu().numpy())
+        np.savez_compressed(os.path.join(out, f"quantize_{name}.npz"), **rec)
+        print("wrote", name)
+    for M, N, K in [(128, 128, 128), (256, 384, 512)]:
+        a, b = gemm_operands(M, N, K)
+        qa = refkernel.quantize_mx(a.cuda())
+        qb = refkernel.quantize_mx(b.cuda())
+        e4, e8 = torch.float8_e4m3fn, torch.float8_e8m0fnu
+        d = torch._scaled_mm(qa[0].view(e4), qb[0].view(e4).t(), qa[1].view(e8), qb[1].view(e8), None, None, torch.float32, False)
+        np.savez_compressed(os.path.join(out, f"gemm_{M}x{N}x{K}.npz"), a=qa[0].cpu().numpy(), a_scale=qa[1].cpu().numpy(),
+                            b=qb[0].cpu().numpy(), b_scale=qb[1].cpu().numpy(), d_f32=d.cpu().numpy())
+        print("wrote gemm", M, N, K)
+
+
+if __name__ == "__main__":
+    main()
