@@ -105,6 +105,25 @@ MXB200_API int mxb200_gemm_splitk(const void* a, const void* a_scale, const void
                        const void* resid, int64_t M, int64_t N, int64_t K, const float* alpha, int accumulate,
                        int splits, void* workspace, size_t workspace_bytes, void* stream);
 
+/* No counterpart in the reference. mxb200_gemm_splitk for callers that have no device memory to hand over and
+ * must not trigger an allocation: a backend wired in at the reference's kernel seam gets plain pointers and a
+ * stream but no workspace argument, runs on autograd worker threads in the middle of backward where a
+ * cudaMalloc would stall the whole device, and in a trainer whose caching allocator already owns all of HBM a
+ * raw allocation simply fails. The partial tiles and tile counters go to an array of
+ * MXB200_STATIC_SCRATCH_BYTES that is part of the library's device image (each GPU that loads the library
+ * carries it for the life of the process). The call itself allocates nothing, on the device or through any
+ * library. Shapes whose mxb200_gemm_workspace_bytes(M, N, K, splits) exceeds that size are refused with
+ * MXB200_ERR_WORKSPACE; pick fewer splits or use mxb200_gemm_splitk. The first call on each device looks up
+ * the array's device address; make that first call outside any stream capture. All calls on a device share
+ * the one array and it keeps whatever the previous call left: the tile counters are cleared on the stream at
+ * the start of every call, the partial tiles are fully rewritten before they are read. Two calls whose kernels
+ * may overlap on the GPU (different streams, no dependency) would race on it; serialise them. Same arguments
+ * and results as mxb200_gemm_splitk, bit for bit. */
+#define MXB200_STATIC_SCRATCH_BYTES (32u << 20)
+MXB200_API int mxb200_gemm_splitk_static(const void* a, const void* a_scale, const void* b, const void* b_scale, void* d,
+                                         int out_kind, const void* resid, int64_t M, int64_t N, int64_t K,
+                                         const float* alpha, int accumulate, int splits, void* stream);
+
 /* Static message for a status (the reference's seam returns const char* messages, mx_gemm_kernel.h:12). */
 MXB200_API const char* mxb200_strerror(int status);
 

@@ -16,11 +16,13 @@ ERR_SHAPE, ERR_ALIGNMENT, ERR_NULL, ERR_ARGUMENT, ERR_WORKSPACE, ERR_DEVICE, ERR
 SCALE_REFERENCE, SCALE_OCP_FLOOR = 0, 1
 PROLOGUE_NONE, PROLOGUE_RELU_SQUARE = 0, 1
 OUT_BF16, OUT_F32 = 0, 1
+STATIC_SCRATCH_BYTES = 32 << 20
 
 # every symbol include/mxb200.h declares
 SYMBOLS = (
     "mxb200_quantize_mx", "mxb200_quantize_mx_relu_square_bwd", "mxb200_gemm_bf16", "mxb200_gemm_f32",
-    "mxb200_gemm_splits", "mxb200_gemm_workspace_bytes", "mxb200_gemm_splitk", "mxb200_strerror",
+    "mxb200_gemm_splits", "mxb200_gemm_workspace_bytes", "mxb200_gemm_splitk", "mxb200_gemm_splitk_static",
+    "mxb200_strerror",
     "mxb200_device_status", "mxb200_set_gemm_config", "mxb200_launch_count", "mxb200_version",
 )
 
@@ -51,6 +53,7 @@ def _load() -> ctypes.CDLL:
     lib.mxb200_gemm_workspace_bytes.argtypes = [i64, i64, i64, i32]
     lib.mxb200_gemm_workspace_bytes.restype = ctypes.c_size_t
     lib.mxb200_gemm_splitk.argtypes = [vp, vp, vp, vp, vp, i32, vp, i64, i64, i64, vp, i32, i32, vp, ctypes.c_size_t, vp]
+    lib.mxb200_gemm_splitk_static.argtypes = [vp, vp, vp, vp, vp, i32, vp, i64, i64, i64, vp, i32, i32, vp]
     lib.mxb200_strerror.argtypes = [i32]
     lib.mxb200_strerror.restype = ctypes.c_char_p
     lib.mxb200_device_status.argtypes = [ctypes.POINTER(ctypes.c_uint32)]

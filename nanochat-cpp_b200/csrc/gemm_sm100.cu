@@ -36,6 +36,11 @@ namespace mxb200 {
 // one watchdog word per device context (module-scope device variable: no allocation)
 __device__ uint32_t g_watchdog_word;
 
+// Split-K scratch for mxb200_gemm_splitk_static: lives in the library's own device image, so every GPU that
+// loads the library holds these bytes until the process exits. In host code this name is only a handle for
+// cudaGetSymbolAddress, never a device pointer.
+static __device__ __align__(256) unsigned char g_static_splitk_scratch[MXB200_STATIC_SCRATCH_BYTES];
+
 namespace {
 
 constexpr int kBM = 128;
@@ -696,4 +701,33 @@ extern "C" int mxb200_device_status(uint32_t* word) {
   if (word != nullptr)
     *word = w;
   return w == 0 ? MXB200_OK : MXB200_ERR_WATCHDOG;
+}
+
+// See include/mxb200.h. Same kernel and same host path as mxb200_gemm_splitk; only the origin of the scratch differs.
+extern "C" int mxb200_gemm_splitk_static(const void* a, const void* a_scale, const void* b, const void* b_scale,
+                                         void* d, int out_kind, const void* resid, int64_t M, int64_t N, int64_t K,
+                                         const float* alpha, int accumulate, int splits, void* stream) {
+  static std::mutex mu;
+  static void* scratch_of_device[64] = {};
+  int device = -1;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64)
+    return MXB200_ERR_DEVICE;
+  void* scratch = nullptr;
+  {
+    // set-up, once per device and with that device current: translate the symbol into this device's address
+    std::lock_guard<std::mutex> lock(mu);
+    if (scratch_of_device[device] == nullptr) {
+      void* p = nullptr;
+      if (cudaGetSymbolAddress(&p, mxb200::g_static_splitk_scratch) != cudaSuccess || p == nullptr) {
+        cudaGetLastError();
+        return MXB200_ERR_DEVICE;
+      }
+      scratch_of_device[device] = p;
+    }
+    scratch = scratch_of_device[device];
+  }
+  if (splits > 1 && mxb200_gemm_workspace_bytes(M, N, K, splits) > MXB200_STATIC_SCRATCH_BYTES)
+    return MXB200_ERR_WORKSPACE;  // the problem needs more scratch than the built-in array holds
+  return mxb200::gemm(a, a_scale, b, b_scale, d, out_kind, resid, M, N, K, alpha, accumulate, splits, scratch,
+                      MXB200_STATIC_SCRATCH_BYTES, stream);
 }
