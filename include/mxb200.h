@@ -132,8 +132,9 @@ MXB200_API const char* mxb200_strerror(int status);
  * Synchronises the device. */
 MXB200_API int mxb200_device_status(uint32_t* word);
 
-/* Tuning knobs for measurement, process-wide: tile width (128 or 256; 0 = choose per shape) and the number of
- * CTAs of the persistent grid (0 = one per SM). Not part of the reference interface. */
+/* Tuning knobs for measurement, process-wide. tile_n: 128 or 256 = the one-CTA kernel with 128 x tile_n tiles;
+ * 384 / 512 = the CTA-pair kernel (256 x 192 / 256 x 256 tile over two SMs); 0 = choose per shape. max_ctas: CTAs of the persistent
+ * grid (0 = one per SM). Not part of the reference interface. */
 MXB200_API int mxb200_set_gemm_config(int tile_n, int max_ctas);
 
 /* How many kernels this library has launched in this process (for benchmark accounting). */

@@ -41,6 +41,15 @@ __device__ uint32_t g_watchdog_word;
 // cudaGetSymbolAddress, never a device pointer.
 static __device__ __align__(256) unsigned char g_static_splitk_scratch[MXB200_STATIC_SCRATCH_BYTES];
 
+#ifdef MXB200_TRACE
+// Development aid (never compiled into the shipped library): per-tile timestamps of the first CTA pair.
+__device__ unsigned long long g_trace[8192];
+#define TRACE(slot, idx) \
+  do { if (blockIdx.x == 0 && (idx) < 64) g_trace[(slot) * 64 + (idx)] = clock64(); } while (0)
+#else
+#define TRACE(slot, idx) do { } while (0)
+#endif
+
 namespace {
 
 constexpr int kBM = 128;
@@ -129,6 +138,11 @@ __device__ __forceinline__ bool wait_bounded(uint64_t* bar, uint32_t parity, Bar
   return true;
 }
 
+// The same wait for a converged warp: every lane polls, the warp agrees on the outcome.
+__device__ __forceinline__ bool wait_bounded_warp(uint64_t* bar, uint32_t parity, Barriers* bars, uint32_t site) {
+  return __all_sync(0xffffffffu, wait_bounded(bar, parity, bars, site)) != 0;
+}
+
 struct TileCoord {
   int m, n, split, tile;
 };
@@ -183,12 +197,14 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   return *reinterpret_cast<const uint32_t*>(&v);
 }
 
-// Final write of 32 consecutive output columns of one row from fp32 values acc[32].
-__device__ __forceinline__ void write_chunk(const GemmParams& p, float alpha, int64_t row, int col, const float* acc) {
+// The output words of 32 consecutive columns of one row from fp32 values acc[32]: 16 words of packed bf16
+// (optionally plus the residual, rounded twice as the reference's separate add) or 32 fp32 words (alpha, +=).
+// `valid` guards the reads of resid / the old output.
+__device__ __forceinline__ void compute_chunk(const GemmParams& p, float alpha, int64_t row, int col, const float* acc,
+                                              bool valid, uint32_t* o) {
   const int64_t idx = row * p.N + col;
   if (p.out_kind == kOutBf16) {
-    uint32_t o[16];
-    if (p.resid != nullptr) {
+    if (p.resid != nullptr && valid) {
       uint32_t rw[16];
       const auto* rp = static_cast<const __nv_bfloat16*>(p.resid) + idx;
       load_u32x8(rp, rw, p.wide);
@@ -205,27 +221,61 @@ __device__ __forceinline__ void write_chunk(const GemmParams& p, float alpha, in
       for (int k = 0; k < 16; ++k)
         o[k] = pack_bf16x2(acc[2 * k], acc[2 * k + 1]);
     }
+  } else {
+    const float* dp = static_cast<const float*>(p.d) + idx;
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      if (p.accumulate && valid) {
+        uint32_t old[8];
+        load_u32x8(dp + 8 * g, old, p.wide);
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          o[8 * g + k] = __float_as_uint(fmaf(alpha, acc[8 * g + k], __uint_as_float(old[k])));
+      } else {
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          o[8 * g + k] = __float_as_uint(alpha * acc[8 * g + k]);
+      }
+    }
+  }
+}
+
+// compute_chunk, then 32-byte stores straight from the thread that owns the row.
+__device__ __forceinline__ void write_chunk(const GemmParams& p, float alpha, int64_t row, int col, const float* acc) {
+  const int64_t idx = row * p.N + col;
+  uint32_t o[32];
+  compute_chunk(p, alpha, row, col, acc, true, o);
+  if (p.out_kind == kOutBf16) {
     auto* dp = static_cast<__nv_bfloat16*>(p.d) + idx;
     store_u32x8(dp, o, p.wide);
     store_u32x8(dp + 16, o + 8, p.wide);
   } else {
     float* dp = static_cast<float*>(p.d) + idx;
 #pragma unroll
-    for (int g = 0; g < 4; ++g) {
-      uint32_t o[8];
-      if (p.accumulate) {
-        uint32_t old[8];
-        load_u32x8(dp + 8 * g, old, p.wide);
+    for (int g = 0; g < 4; ++g)
+      store_u32x8(dp + 8 * g, o + 8 * g, p.wide);
+  }
+}
+
+// A warp's 32 rows x 64 bytes leave through shared memory and one TMA store: each lane parks its row's 64 bytes
+// (16-byte pieces placed by the 64-byte swizzle the tensor map expects, which also spreads the lanes over the
+// banks), the warp syncs, one lane issues the store. The TMA engine writes whole contiguous row segments,
+// where per-thread stores of one row each reach L2 as 32 scattered sectors per instruction and back up the SM's
+// store path. `issue` false: rows or columns past the matrix, nothing to write.
+__device__ __forceinline__ void store_rows_tma(const CUtensorMap* map_d, unsigned char* stage, int lane,
+                                               const uint32_t* w, int x, int y, bool issue) {
+  if (lane == 0)
+    tma_store_wait_read<0>();  // the previous store from this buffer has been read out
+  __syncwarp();
 #pragma unroll
-        for (int k = 0; k < 8; ++k)
-          o[k] = __float_as_uint(fmaf(alpha, acc[8 * g + k], __uint_as_float(old[k])));
-      } else {
-#pragma unroll
-        for (int k = 0; k < 8; ++k)
-          o[k] = __float_as_uint(alpha * acc[8 * g + k]);
-      }
-      store_u32x8(dp + 8 * g, o, p.wide);
-    }
+  for (int j = 0; j < 4; ++j)
+    *reinterpret_cast<uint4*>(stage + lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4)) =
+          make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+  fence_proxy_async_smem();
+  __syncwarp();
+  if (lane == 0 && issue) {
+    tma_store_2d(map_d, stage, x, y);
+    tma_store_commit();
   }
 }
 
@@ -273,8 +323,9 @@ __global__ void __launch_bounds__(kThreads, 1)
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&bars->tmem_base);
 
   if (warp == 0) {
-    // ------------------------------------------------------------------ producer
-    if (lane == 0) {
+    // ------------------------------------------------------------------ producer (whole warp, one lane issues)
+    {
+      const uint32_t el = elect_one() ? 1u : 0u;
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -288,18 +339,18 @@ __global__ void __launch_bounds__(kThreads, 1)
         const uint8_t* sfa_src = p.a_scale + static_cast<int64_t>(tc.m) * p.k_tiles_total * kScaleTileBytes;
         const uint8_t* sfb_src = p.b_scale + static_cast<int64_t>(tc.n) * C::kSfbTiles * p.k_tiles_total * kScaleTileBytes;
         for (int kt = k_begin; kt < k_end; ++kt) {
-          if (!wait_bounded(&bars->empty[stage], phase ^ 1u, bars, kSiteProducerEmpty)) {
+          if (!wait_bounded_warp(&bars->empty[stage], phase ^ 1u, bars, kSiteProducerEmpty)) {
             ok = false;
             break;
           }
           uint64_t* full = &bars->full[stage];
-          mbar_arrive_expect_tx(full, tx);
-          tma_load_2d(s_a + stage * C::kABytes, &map_a, full, kt * kBK, tc.m * kBM);
-          tma_load_2d(s_b + stage * C::kBBytes, &map_b, full, kt * kBK, tc.n * BN);
+          mbar_arrive_expect_tx(el, full, tx);
+          tma_load_2d(el, s_a + stage * C::kABytes, &map_a, full, kt * kBK, tc.m * kBM);
+          tma_load_2d(el, s_b + stage * C::kBBytes, &map_b, full, kt * kBK, tc.n * BN);
           unsigned char* sf = s_sf + stage * C::kSfBytes;
-          bulk_load(sf, sfa_src + static_cast<int64_t>(kt) * kScaleTileBytes, kScaleTileBytes, full);
+          bulk_load(el, sf, sfa_src + static_cast<int64_t>(kt) * kScaleTileBytes, kScaleTileBytes, full);
           for (int j = 0; j < sfb_tiles; ++j)
-            bulk_load(sf + (1 + j) * kScaleTileBytes,
+            bulk_load(el, sf + (1 + j) * kScaleTileBytes,
                       sfb_src + (static_cast<int64_t>(j) * p.k_tiles_total + kt) * kScaleTileBytes, kScaleTileBytes,
                       full);
           if (++stage == C::kStages) {
@@ -310,8 +361,9 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
     }
   } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    // ------------------------------------------------------------------ MMA issuer (whole warp, one lane issues)
+    {
+      const uint32_t el = elect_one() ? 1u : 0u;
       int stage = 0;
       uint32_t phase = 0;
       uint32_t local = 0;  // tiles this CTA has started
@@ -325,13 +377,13 @@ __global__ void __launch_bounds__(kThreads, 1)
         const uint32_t idesc = make_idesc_mxf8(kBM, static_cast<uint32_t>(n_valid));
         const uint32_t buf = local & 1u, use = local >> 1;
         // the buffer's previous tile (two tiles ago) must be drained ...
-        if (!wait_bounded(&bars->tmem_empty[buf], (use & 1u) ^ 1u, bars, kSiteMmaTmemEmpty)) {
+        if (!wait_bounded_warp(&bars->tmem_empty[buf], (use & 1u) ^ 1u, bars, kSiteMmaTmemEmpty)) {
           ok = false;
           break;
         }
         // ... and, with overlapping buffers, the previous tile must have given up the shared columns
         if (C::kOverlap && local > 0) {
-          if (!wait_bounded(&bars->overlap_free, (local - 1) & 1u, bars, kSiteMmaOverlap)) {
+          if (!wait_bounded_warp(&bars->overlap_free, (local - 1) & 1u, bars, kSiteMmaOverlap)) {
             ok = false;
             break;
           }
@@ -341,33 +393,33 @@ __global__ void __launch_bounds__(kThreads, 1)
         const int k_begin = tc.split * p.k_tiles_split;
         const int k_end = min(k_begin + p.k_tiles_split, p.k_tiles_total);
         for (int kt = k_begin; kt < k_end; ++kt) {
-          if (!wait_bounded(&bars->full[stage], phase, bars, kSiteMmaFull)) {
+          if (!wait_bounded_warp(&bars->full[stage], phase, bars, kSiteMmaFull)) {
             ok = false;
             break;
           }
           tcgen05_fence_after_sync();
           const uint32_t sf_addr = smem_u32(s_sf + stage * C::kSfBytes);
           // scale tiles: 32 rows x 16 bytes, 8-row groups 128 bytes apart, no swizzle
-          tcgen05_cp_32x128b_warpx4(sfa_t, make_smem_desc(sf_addr, 0, 128, 0));
+          tcgen05_cp_32x128b_warpx4(el, sfa_t, make_smem_desc(sf_addr, 0, 128, 0));
           for (int j = 0; j < sfb_tiles; ++j)
-            tcgen05_cp_32x128b_warpx4(sfb_t + 4 * j, make_smem_desc(sf_addr + (1 + j) * kScaleTileBytes, 0, 128, 0));
+            tcgen05_cp_32x128b_warpx4(el, sfb_t + 4 * j, make_smem_desc(sf_addr + (1 + j) * kScaleTileBytes, 0, 128, 0));
           // operand tiles: K-major, 128-byte swizzle, 8-row groups 1024 bytes apart
           const uint64_t a_desc = make_smem_desc(smem_u32(s_a + stage * C::kABytes), 16, 1024, 2);
           const uint64_t b_desc = make_smem_desc(smem_u32(s_b + stage * C::kBBytes), 16, 1024, 2);
 #pragma unroll
           for (uint32_t k = 0; k < 4; ++k) {
             // K = 32 per step: 32 bytes further into the swizzle atom; scale byte k of the 32-bit column
-            tcgen05_mma_mxf8(acc_t, a_desc + 2 * k, b_desc + 2 * k, idesc_with_sf(idesc, k, k), sfa_t, sfb_t,
+            tcgen05_mma_mxf8(el, acc_t, a_desc + 2 * k, b_desc + 2 * k, idesc_with_sf(idesc, k, k), sfa_t, sfb_t,
                              (kt > k_begin || k > 0) ? 1u : 0u);
           }
-          tcgen05_commit(&bars->empty[stage]);
+          tcgen05_commit(el, &bars->empty[stage]);
           if (++stage == C::kStages) {
             stage = 0;
             phase ^= 1u;
           }
         }
         if (ok)
-          tcgen05_commit(&bars->tmem_full[buf]);
+          tcgen05_commit(el, &bars->tmem_full[buf]);
       }
     }
   } else {
@@ -491,6 +543,352 @@ __global__ void __launch_bounds__(kThreads, 1)
   }
 }
 
+
+// ------------------------------------------------------------------------------------------------ CTA-pair kernel
+//
+// Two CTAs on the SMs of one TPC (a cluster of 2) share one 256 x 256 output tile: tcgen05.mma.cta_group::2 reads
+// 128 rows of A and 128 rows of B from each CTA's shared memory and leaves each CTA its own 128 rows of the
+// accumulator in its own TMEM. Per K step every CTA therefore loads 16 KB of A and 16 KB of B for 128 x 256 x 128
+// multiply-adds: half the L2-to-SM traffic per flop of the one-CTA kernel, and a 34 KB stage, so 6 stages fit.
+// Both CTAs run the same three roles. Each loads its own halves (tiled loads, the byte counts credited to the
+// leader's full barrier); only the leader (cluster rank 0) issues tcgen05.cp / tcgen05.mma, and its commits
+// arrive on both CTAs' empty / tmem_full barriers; each CTA's epilogue drains its own TMEM and reports to the
+// leader's tmem_empty / overlap barriers. Scale tiles come through tensor maps too, so rows past the end of a
+// matrix read as zero scales (2^-127) against zero data instead of touching memory out of range.
+
+// TN = 256: the widest tile (least L2 traffic per flop); its two accumulator buffers overlap by 32 columns, so
+// the next tile's first MMA waits until the previous tile's epilogue has read those columns: a bubble of several
+// hundred cycles per tile, negligible for long K. TN = 192: two disjoint 192-column buffers, no bubble, for
+// shapes with a short main loop. Scale tiles of B are always loaded as the two 128-row tiles covering the tile's
+// columns; an odd 192-wide tile starts 64 rows into the first one, i.e. 2 TMEM columns in.
+constexpr int kEpiStageBytes = 2048;       // one epilogue warp's staging buffer for TMA stores
+constexpr int kPairThreads = 320;          // producer warp, MMA warp, 8 epilogue warps
+constexpr int kPairEpilogueThreads = 256;  // two warps per TMEM lane quarter, each half of the tile's columns
+
+template <int TN>
+struct PairConfig {
+  static_assert(TN == 192 || TN == 256, "tile width");
+  static constexpr int kTileM = 256, kTileN = TN;
+  static constexpr int kBRows = TN / 2;                // this CTA's rows of B
+  static constexpr uint32_t kABytes = 128 * kBK;       // this CTA's 128 rows of A
+  static constexpr uint32_t kBBytes = kBRows * kBK;
+  static constexpr uint32_t kSfBytes = kScaleTileBytes * 3;  // A: own 128 rows; B: two tiles
+  static constexpr uint32_t kTxPerCta = kABytes + kBBytes + kSfBytes;
+  static constexpr int kStages = TN == 256 ? 6 : 7;
+  static constexpr bool kOverlap = TN == 256;
+  static constexpr uint32_t kAcc0 = 0, kAcc1 = kOverlap ? 224 : TN;
+  static constexpr uint32_t kSfaCol = kOverlap ? 480 : 2 * TN, kSfbCol = kSfaCol + 4;
+  static constexpr size_t kSmemBytes = 1024 + static_cast<size_t>(kStages) * (kABytes + kBBytes + kSfBytes) +
+                                       kPairEpilogueThreads / 32 * kEpiStageBytes + 256;
+};
+
+template <int TN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
+      mxb200_mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                                 const __grid_constant__ CUtensorMap map_sfa,
+                                 const __grid_constant__ CUtensorMap map_sfb,
+                                 const __grid_constant__ CUtensorMap map_d, const GemmParams p) {
+  using C = PairConfig<TN>;
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  unsigned char* s_a = smem;
+  unsigned char* s_b = s_a + C::kStages * C::kABytes;
+  unsigned char* s_epi = s_b + C::kStages * C::kBBytes;  // 2 KB per epilogue warp: 32 rows x 64 bytes
+  unsigned char* s_sf = s_epi + kPairEpilogueThreads / 32 * kEpiStageBytes;  // per stage: A's tile, B's two tiles
+  Barriers* bars = reinterpret_cast<Barriers*>(s_sf + C::kStages * C::kSfBytes);
+
+  const int warp = static_cast<int>(threadIdx.x) >> 5, lane = static_cast<int>(threadIdx.x) & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+  const int pair = static_cast<int>(blockIdx.x) >> 1, num_pairs = static_cast<int>(gridDim.x) >> 1;
+  const int total_units = p.tiles_m * p.tiles_n * p.splits;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::kStages; ++s) {
+      mbar_init(&bars->full[s], 1);
+      mbar_init(&bars->empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&bars->tmem_full[a], 1);
+      mbar_init(&bars->tmem_empty[a], 16);  // one arrival per epilogue warp of either CTA (leader's copy is used)
+    }
+    mbar_init(&bars->overlap_free, 8);  // the four warps per CTA that own the shared columns
+    mbar_init(&bars->epi_sync, kPairEpilogueThreads);
+    bars->abort_flag = 0;
+    bars->last_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 0 && lane == 0) {
+    prefetch_tensormap(&map_a);
+    prefetch_tensormap(&map_b);
+    prefetch_tensormap(&map_sfa);
+    prefetch_tensormap(&map_sfb);
+    prefetch_tensormap(&map_d);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(&bars->tmem_base, kTmemCols);
+    tmem_relinquish_pair();
+  }
+  tcgen05_fence_before_sync();
+  __syncthreads();
+  cluster_arrive();  // the peer's barriers exist before anything is credited to them
+  cluster_wait();
+  tcgen05_fence_after_sync();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&bars->tmem_base);
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ producer (both CTAs; one lane issues)
+    {
+      const uint32_t el = elect_one() ? 1u : 0u;
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int unit = pair; ok && unit < total_units; unit += num_pairs) {
+        const TileCoord tc = decode_unit(p, unit);
+        const int k_begin = tc.split * p.k_tiles_split;
+        const int k_end = min(k_begin + p.k_tiles_split, p.k_tiles_total);
+        const int row_a = tc.m * C::kTileM + static_cast<int>(rank) * 128;
+        const int row_b = tc.n * C::kTileN + static_cast<int>(rank) * C::kBRows;
+        if (el) TRACE(4, (unit - pair) / num_pairs);
+        for (int kt = k_begin; kt < k_end; ++kt) {
+          if (!wait_bounded_warp(&bars->empty[stage], phase ^ 1u, bars, kSiteProducerEmpty)) {
+            ok = false;
+            break;
+          }
+          mbar_arrive_expect_tx(leader ? el : 0u, &bars->full[stage], 2 * C::kTxPerCta);
+          const uint32_t full = map_to_cta(smem_u32(&bars->full[stage]), 0);
+          tma_load_2d_pair(el, s_a + stage * C::kABytes, &map_a, full, kt * kBK, row_a);
+          tma_load_2d_pair(el, s_b + stage * C::kBBytes, &map_b, full, kt * kBK, row_b);
+          unsigned char* sf = s_sf + stage * C::kSfBytes;
+          tma_load_4d_pair(el, sf, &map_sfa, full, 0, 0, kt, row_a >> 7);
+          tma_load_4d_pair(el, sf + kScaleTileBytes, &map_sfb, full, 0, 0, kt, (tc.n * C::kTileN) >> 7);
+          if (++stage == C::kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer (leader CTA only)
+    if (leader) {
+      const uint32_t el = elect_one() ? 1u : 0u;
+      int stage = 0;
+      uint32_t phase = 0;
+      uint32_t local = 0;
+      bool ok = true;
+      const uint32_t sfa_t = tmem_base + C::kSfaCol, sfb_t = tmem_base + C::kSfbCol;
+      const uint32_t idesc = make_idesc_mxf8(C::kTileM, C::kTileN);
+      for (int unit = pair; ok && unit < total_units; unit += num_pairs, ++local) {
+        const TileCoord tc = decode_unit(p, unit);
+        const uint32_t buf = local & 1u, use = local >> 1;
+        if (!wait_bounded_warp(&bars->tmem_empty[buf], (use & 1u) ^ 1u, bars, kSiteMmaTmemEmpty)) {
+          ok = false;
+          break;
+        }
+        if (C::kOverlap && local > 0 &&
+            !wait_bounded_warp(&bars->overlap_free, (local - 1) & 1u, bars, kSiteMmaOverlap)) {
+          ok = false;
+          break;
+        }
+        tcgen05_fence_after_sync();
+        if (el) TRACE(0, local);
+        const uint32_t acc_t = tmem_base + (buf ? C::kAcc1 : C::kAcc0);
+        // the tile's first column is ((n * TN) % 128) / 32 scale columns into the first of B's two tiles
+        const uint32_t sfb_mma = sfb_t + static_cast<uint32_t>(((tc.n * C::kTileN) & 127) >> 5);
+        const int k_begin = tc.split * p.k_tiles_split;
+        const int k_end = min(k_begin + p.k_tiles_split, p.k_tiles_total);
+        for (int kt = k_begin; kt < k_end; ++kt) {
+          if (!wait_bounded_warp(&bars->full[stage], phase, bars, kSiteMmaFull)) {
+            ok = false;
+            break;
+          }
+          tcgen05_fence_after_sync();
+          const uint32_t sf_addr = smem_u32(s_sf + stage * C::kSfBytes);
+          tcgen05_cp_32x128b_warpx4_pair(el, sfa_t, make_smem_desc(sf_addr, 0, 128, 0));
+          tcgen05_cp_32x128b_warpx4_pair(el, sfb_t, make_smem_desc(sf_addr + kScaleTileBytes, 0, 128, 0));
+          tcgen05_cp_32x128b_warpx4_pair(el, sfb_t + 4, make_smem_desc(sf_addr + 2 * kScaleTileBytes, 0, 128, 0));
+          const uint64_t a_desc = make_smem_desc(smem_u32(s_a + stage * C::kABytes), 16, 1024, 2);
+          const uint64_t b_desc = make_smem_desc(smem_u32(s_b + stage * C::kBBytes), 16, 1024, 2);
+#pragma unroll
+          for (uint32_t k = 0; k < 4; ++k)
+            tcgen05_mma_mxf8_pair(el, acc_t, a_desc + 2 * k, b_desc + 2 * k, idesc_with_sf(idesc, k, k), sfa_t, sfb_mma,
+                                  (kt > k_begin || k > 0) ? 1u : 0u);
+          tcgen05_commit_pair(el, &bars->empty[stage], 3);  // frees this stage in both CTAs
+          if (++stage == C::kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (ok)
+          tcgen05_commit_pair(el, &bars->tmem_full[buf], 3);
+        if (el) TRACE(1, local);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..9, both CTAs)
+    // A warp may read only the TMEM lanes of its quarter (warp id % 4); two warps share each quarter and take
+    // one half of the tile's columns each. TMEM loads are software-pipelined: the next 32 columns are in flight
+    // while the current 32 are converted and stored.
+    const int quarter = warp & 3;
+    const int col_half = (warp - 2) >> 2;
+    const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
+    const float alpha = (p.out_kind == kOutF32 && p.alpha != nullptr) ? *p.alpha : 1.f;
+    uint32_t local = 0, sync_phase = 0;
+    bool ok = true;
+    constexpr int kChunks = C::kTileN / 32;
+    constexpr int kMine = kChunks / 2;      // chunks per warp
+    constexpr int kHalf = 128 * C::kTileN;  // elements of one CTA's half tile
+    const uint32_t empty_leader[2] = {map_to_cta(smem_u32(&bars->tmem_empty[0]), 0),
+                                      map_to_cta(smem_u32(&bars->tmem_empty[1]), 0)};
+    const uint32_t overlap_leader = map_to_cta(smem_u32(&bars->overlap_free), 0);
+    unsigned char* stage = s_epi + (warp - 2) * kEpiStageBytes;
+    for (int unit = pair; ok && unit < total_units; unit += num_pairs, ++local) {
+      const TileCoord tc = decode_unit(p, unit);
+      const uint32_t buf = local & 1u, use = local >> 1;
+      if (!wait_bounded(&bars->tmem_full[buf], use & 1u, bars, kSiteEpilogueFull)) {
+        ok = false;
+        break;
+      }
+      tcgen05_fence_after_sync();
+      if (threadIdx.x == 64) TRACE(2, local);
+      const uint32_t acc_t = tmem_base + lane_base + (buf ? C::kAcc1 : C::kAcc0);
+      const int64_t row = static_cast<int64_t>(tc.m) * C::kTileM + rank * 128 + quarter * 32 + lane;
+      const bool row_ok = row < p.M;
+      const int warp_row0 = tc.m * C::kTileM + static_cast<int>(rank) * 128 + quarter * 32;
+      const int col0 = tc.n * C::kTileN;
+      const int64_t half_index = (static_cast<int64_t>(tc.tile) * p.splits + tc.split) * 2 + rank;
+      float* part = p.splits > 1 ? p.partials + half_index * kHalf + static_cast<int64_t>(quarter * 32 + lane) * C::kTileN
+                                 : nullptr;
+      // Overlapping buffers: buffer 0 shares its last 32 columns (owned by column half 1), buffer 1 its first 32
+      // (column half 0). The owning warps read those first and hand them over before anything else.
+      const bool owns_shared = C::kOverlap && ((buf == 0) == (col_half == 1));
+      auto chunk_of = [&](int i) {
+        if (C::kOverlap && buf == 0 && col_half == 1)
+          return i == 0 ? kChunks - 1 : kMine + i - 1;
+        return col_half * kMine + i;
+      };
+      uint32_t r[2][32];
+      tmem_ld_32x32b_x32(acc_t + chunk_of(0) * 32, r[0]);
+#pragma unroll
+      for (int i = 0; i < kMine; ++i) {
+        const int c = chunk_of(i);
+        tmem_ld_wait();
+        if (threadIdx.x == 64 && i == 0) TRACE(5, local);
+        if (threadIdx.x == 64 && i == 1) TRACE(6, local);
+        if (threadIdx.x == 64 && i == 2) TRACE(7, local);
+        if (i + 1 < kMine)
+          tmem_ld_32x32b_x32(acc_t + chunk_of(i + 1) * 32, r[(i + 1) & 1]);
+        if (i == 0 && owns_shared) {
+          tcgen05_fence_before_sync();
+          __syncwarp();
+          if (lane == 0)
+            mbar_arrive_cluster(overlap_leader);
+        }
+        const int col = col0 + c * 32;
+        if (part != nullptr) {
+          if (row_ok && col < p.N) {
+#pragma unroll
+            for (int g = 0; g < 4; ++g)
+              store_u32x8(part + c * 32 + 8 * g, r[i & 1] + 8 * g, true);
+          }
+        } else {
+          const bool valid = row_ok && col < p.N;
+          const bool issue = warp_row0 < p.M && col < p.N;
+          uint32_t o[32];
+          compute_chunk(p, alpha, row, col, reinterpret_cast<const float*>(r[i & 1]), valid, o);
+          if (threadIdx.x == 64 && i == 2) TRACE(8, local);
+          store_rows_tma(&map_d, stage, lane, o, col, warp_row0, issue);
+          if (threadIdx.x == 64 && i == 2) TRACE(9, local);
+          if (p.out_kind == kOutF32)
+            store_rows_tma(&map_d, stage, lane, o + 16, col + 16, warp_row0, issue);
+        }
+      }
+      tcgen05_fence_before_sync();
+      __syncwarp();
+      if (threadIdx.x == 64) TRACE(10, local);
+      if (lane == 0)
+        mbar_arrive_cluster(empty_leader[buf]);
+      if (threadIdx.x == 64) TRACE(3, local);
+
+      if (part != nullptr) {
+        // split-K, per half tile: the rows of this CTA are reduced by whichever CTA finishes them last
+        __threadfence();
+        mbar_arrive(&bars->epi_sync);
+        if (!wait_bounded(&bars->epi_sync, sync_phase, bars, kSiteEpilogueSync)) {
+          ok = false;
+          break;
+        }
+        sync_phase ^= 1u;
+        if (threadIdx.x == 64) {
+          uint32_t* counter = &p.counters[tc.tile * 2 + rank];
+          const uint32_t prev = atomicAdd(counter, 1u);
+          const bool last = prev + 1 == static_cast<uint32_t>(p.splits);
+          if (last)
+            *counter = 0;
+          *reinterpret_cast<volatile uint32_t*>(&bars->last_flag) = last ? 1u : 0u;
+        }
+        mbar_arrive(&bars->epi_sync);
+        if (!wait_bounded(&bars->epi_sync, sync_phase, bars, kSiteEpilogueSync)) {
+          ok = false;
+          break;
+        }
+        sync_phase ^= 1u;
+        const bool last = *reinterpret_cast<volatile uint32_t*>(&bars->last_flag) != 0;
+        if (last && row_ok) {
+          __threadfence();
+          const float* tile_part = p.partials + (static_cast<int64_t>(tc.tile) * p.splits * 2 + rank) * kHalf +
+                                   static_cast<int64_t>(quarter * 32 + lane) * C::kTileN;
+#pragma unroll 1
+          for (int c = col_half * kMine; c < (col_half + 1) * kMine; ++c) {
+            if (col0 + c * 32 >= p.N)
+              break;
+            float acc[32];
+#pragma unroll
+            for (int k = 0; k < 32; ++k)
+              acc[k] = 0.f;
+            for (int s = 0; s < p.splits; ++s) {
+              const float* src = tile_part + static_cast<int64_t>(s) * 2 * kHalf + c * 32;
+#pragma unroll
+              for (int g = 0; g < 4; ++g) {
+                uint32_t w[8];
+                load_u32x8_cg(src + 8 * g, w);
+#pragma unroll
+                for (int k = 0; k < 8; ++k)
+                  acc[8 * g + k] += __uint_as_float(w[k]);
+              }
+            }
+            write_chunk(p, alpha, row, col0 + c * 32, acc);
+          }
+        }
+        mbar_arrive(&bars->epi_sync);
+        if (!wait_bounded(&bars->epi_sync, sync_phase, bars, kSiteEpilogueSync)) {
+          ok = false;
+          break;
+        }
+        sync_phase ^= 1u;
+      }
+    }
+  }
+
+  if (*reinterpret_cast<volatile uint32_t*>(&bars->abort_flag) != 0) {
+    const uint64_t t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 200000ull) {
+    }
+  }
+  if (warp >= 2 && lane == 0)
+    tma_store_wait_all<0>();  // this warp's output stores have left shared memory and reached global memory
+  // neither CTA may leave while the other can still read its shared memory or signal its barriers
+  tcgen05_fence_before_sync();
+  __syncthreads();
+  cluster_arrive();
+  cluster_wait();
+  if (warp == 1) {
+    tcgen05_fence_after_sync();
+    tmem_dealloc_pair(tmem_base, kTmemCols);
+  }
+}
+
 // ------------------------------------------------------------------------------------------------ host side
 
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -524,38 +922,115 @@ int make_operand_map(CUtensorMap* map, const void* base, int64_t rows, int64_t k
   return r == CUDA_SUCCESS ? MXB200_OK : MXB200_ERR_DRIVER;
 }
 
+// (M, N) row-major output, box = 32 rows x 64 bytes (32 bf16 or 16 fp32 columns), 64-byte swizzle: the shape one
+// epilogue warp stores at a time.
+int make_output_map(CUtensorMap* map, void* base, int64_t M, int64_t N, bool f32) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr)
+    return MXB200_ERR_DRIVER;
+  const cuuint64_t esize = f32 ? 4 : 2;
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(N), static_cast<cuuint64_t>(M)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(N) * esize};
+  const cuuint32_t box[2] = {static_cast<cuuint32_t>(64 / esize), 32};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = fn(map, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, base, dims,
+                        strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B,
+                        CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? MXB200_OK : MXB200_ERR_DRIVER;
+}
+
 std::atomic<int> g_tile_n{0};
 std::atomic<int> g_max_ctas{0};
 
-int choose_bn(int64_t N) {
+// (rows / 128, k / 128) scale tiles of 32 x 16 bytes each, as a 4-D tensor {16, 32, k tiles, row tiles}; the box
+// takes `tiles` row tiles of one k tile, i.e. tiles x 512 contiguous bytes in shared memory.
+int make_scale_map(CUtensorMap* map, const void* base, int64_t rows, int64_t k, int tiles) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr)
+    return MXB200_ERR_DRIVER;
+  const cuuint64_t kt = static_cast<cuuint64_t>(k / 128), rt = static_cast<cuuint64_t>(rows / 128);
+  const cuuint64_t dims[4] = {16, 32, kt, rt};
+  const cuuint64_t strides[3] = {16, 512, 512 * kt};
+  const cuuint32_t box[4] = {16, 32, 1, static_cast<cuuint32_t>(tiles)};
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
+  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void*>(base), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? MXB200_OK : MXB200_ERR_DRIVER;
+}
+
+// How a shape is tiled: one-CTA kernel with 128 x 128 or 128 x 256 tiles, or the CTA-pair kernel with 256 x 192
+// or 256 x 256.
+struct TilePlan {
+  bool pair;
+  int tile_m, tile_n;
+  int slots;         // tiles the machine runs at once
+  int64_t tiles_m, tiles_n;
+  int64_t tiles() const { return tiles_m * tiles_n; }
+  size_t tile_bytes() const { return static_cast<size_t>(tile_m) * tile_n * sizeof(float); }
+  int64_t counters() const { return tiles() * (pair ? 2 : 1); }
+};
+
+TilePlan plan_tiles(int64_t M, int64_t N, int64_t K, int sms) {
   const int forced = g_tile_n.load();
-  if (forced == 128 || forced == 256)
-    return forced;
-  return N >= 256 ? 256 : 128;
+  TilePlan t{};
+  if (forced == 512 || forced == 384 || (forced == 0 && M >= 256 && N >= 256)) {
+    t.pair = true, t.tile_m = 256, t.slots = std::max(sms / 2, 1);
+    // a short main loop cannot hide the 256-wide tile's hand-over bubble; take 192 when it tiles N well
+    const int64_t n192 = (N + 191) / 192 * 192;
+    const bool narrow = K <= 4096 && n192 * 20 <= N * 21;
+    t.tile_n = forced == 512 ? 256 : (forced == 384 ? 192 : (narrow ? 192 : 256));
+  } else {
+    t.pair = false, t.tile_m = 128, t.slots = std::max(sms, 1);
+    t.tile_n = (forced == 128 || forced == 256) ? forced : (N >= 256 ? 256 : 128);
+  }
+  t.tiles_m = (M + t.tile_m - 1) / t.tile_m;
+  t.tiles_n = (N + t.tile_n - 1) / t.tile_n;
+  return t;
+}
+
+size_t counters_bytes(int64_t counters) {
+  return static_cast<size_t>((counters * 4 + 255) / 256 * 256);
+}
+
+size_t workspace_bytes_for(const TilePlan& t, int splits) {
+  return splits <= 1 ? 0 : counters_bytes(t.counters()) + static_cast<size_t>(t.tiles()) * splits * t.tile_bytes();
+}
+
+template <typename Kernel>
+int set_smem_once(Kernel kernel, size_t bytes, bool* configured) {
+  static std::mutex mu;
+  int device = 0;
+  cudaGetDevice(&device);
+  std::lock_guard<std::mutex> lock(mu);
+  if (device < 64 && !configured[device]) {
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes)) != cudaSuccess)
+      return MXB200_ERR_LAUNCH;
+    configured[device] = true;
+  }
+  return MXB200_OK;
 }
 
 template <int BN>
 int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, int grid, cudaStream_t stream) {
-  static std::mutex mu;
   static bool configured[64] = {};
-  int device = 0;
-  cudaGetDevice(&device);
-  {
-    std::lock_guard<std::mutex> lock(mu);
-    if (device < 64 && !configured[device]) {
-      if (cudaFuncSetAttribute(mxb200_mx_gemm_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                               static_cast<int>(Config<BN>::kSmemBytes)) != cudaSuccess)
-        return MXB200_ERR_LAUNCH;
-      configured[device] = true;
-    }
-  }
+  if (int st = set_smem_once(mxb200_mx_gemm_kernel<BN>, Config<BN>::kSmemBytes, configured); st != MXB200_OK)
+    return st;
   mxb200_mx_gemm_kernel<BN><<<grid, kThreads, Config<BN>::kSmemBytes, stream>>>(ma, mb, p);
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return launch_status();
 }
 
-size_t counters_bytes(int64_t tiles) {
-  return static_cast<size_t>((tiles * 4 + 255) / 256 * 256);
+template <int TN>
+int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& msa, const CUtensorMap& msb,
+                const CUtensorMap& md, const GemmParams& p, int pairs, cudaStream_t stream) {
+  static bool configured[64] = {};
+  if (int st = set_smem_once(mxb200_mx_gemm_pair_kernel<TN>, PairConfig<TN>::kSmemBytes, configured); st != MXB200_OK)
+    return st;
+  mxb200_mx_gemm_pair_kernel<TN><<<2 * pairs, kPairThreads, PairConfig<TN>::kSmemBytes, stream>>>(ma, mb, msa, msb, md,
+                                                                                                 p);
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return launch_status();
 }
 
 int gemm(const void* a, const void* a_scale, const void* b, const void* b_scale, void* d, int out_kind,
@@ -580,7 +1055,7 @@ int gemm(const void* a, const void* a_scale, const void* b, const void* b_scale,
   if (splits < 1 || splits > k_tiles || splits > 64)
     return MXB200_ERR_ARGUMENT;
 
-  const int bn = choose_bn(N);
+  const TilePlan plan = plan_tiles(M, N, K, dev.sms);
   GemmParams p{};
   p.a_scale = static_cast<const uint8_t*>(a_scale);
   p.b_scale = static_cast<const uint8_t*>(b_scale);
@@ -588,8 +1063,8 @@ int gemm(const void* a, const void* a_scale, const void* b, const void* b_scale,
   p.resid = out_kind == kOutBf16 ? resid : nullptr;
   p.alpha = out_kind == kOutF32 ? alpha : nullptr;
   p.M = static_cast<int>(M), p.N = static_cast<int>(N), p.K = static_cast<int>(K);
-  p.tiles_m = static_cast<int>(M / kBM);
-  p.tiles_n = static_cast<int>((N + bn - 1) / bn);
+  p.tiles_m = static_cast<int>(plan.tiles_m);
+  p.tiles_n = static_cast<int>(plan.tiles_n);
   p.k_tiles_total = k_tiles;
   p.k_tiles_split = (k_tiles + splits - 1) / splits;
   p.splits = (k_tiles + p.k_tiles_split - 1) / p.k_tiles_split;  // no empty slices
@@ -597,29 +1072,45 @@ int gemm(const void* a, const void* a_scale, const void* b, const void* b_scale,
   p.out_kind = out_kind;
   p.accumulate = out_kind == kOutF32 ? (accumulate != 0) : 0;
   p.wide = (reinterpret_cast<uintptr_t>(d) & 31u) == 0 && (reinterpret_cast<uintptr_t>(resid) & 31u) == 0;
-  const int64_t tiles = static_cast<int64_t>(p.tiles_m) * p.tiles_n;
+  const int64_t tiles = plan.tiles();
   if (tiles * p.splits > 0x7fffffffLL)
     return MXB200_ERR_SHAPE;
   auto* s = static_cast<cudaStream_t>(stream);
   if (p.splits > 1) {
-    const size_t need = counters_bytes(tiles) + static_cast<size_t>(tiles) * p.splits * kBM * bn * sizeof(float);
+    const size_t need = workspace_bytes_for(plan, p.splits);
     if (workspace == nullptr || workspace_bytes < need)
       return MXB200_ERR_WORKSPACE;
     if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0)
       return MXB200_ERR_ALIGNMENT;
     p.counters = static_cast<uint32_t*>(workspace);
-    p.partials = reinterpret_cast<float*>(static_cast<unsigned char*>(workspace) + counters_bytes(tiles));
-    if (cudaMemsetAsync(p.counters, 0, counters_bytes(tiles), s) != cudaSuccess)
+    p.partials = reinterpret_cast<float*>(static_cast<unsigned char*>(workspace) + counters_bytes(plan.counters()));
+    if (cudaMemsetAsync(p.counters, 0, counters_bytes(plan.counters()), s) != cudaSuccess)
       return MXB200_ERR_LAUNCH;
   }
+  const int cap = g_max_ctas.load() > 0 ? g_max_ctas.load() : dev.sms;
   CUtensorMap ma, mb;
+  if (plan.pair) {
+    CUtensorMap msa, msb, md;
+    if (int st = make_output_map(&md, d, M, N, out_kind == kOutF32); st != MXB200_OK)
+      return st;
+    if (int st = make_operand_map(&ma, a, M, K, 128); st != MXB200_OK)
+      return st;
+    if (int st = make_operand_map(&mb, b, N, K, plan.tile_n / 2); st != MXB200_OK)
+      return st;
+    if (int st = make_scale_map(&msa, a_scale, M, K, 1); st != MXB200_OK)
+      return st;
+    if (int st = make_scale_map(&msb, b_scale, N, K, 2); st != MXB200_OK)
+      return st;
+    const int pairs = static_cast<int>(std::min<int64_t>(tiles * p.splits, std::max(cap / 2, 1)));
+    return plan.tile_n == 256 ? launch_pair<256>(ma, mb, msa, msb, md, p, pairs, s)
+                              : launch_pair<192>(ma, mb, msa, msb, md, p, pairs, s);
+  }
   if (int st = make_operand_map(&ma, a, M, K, kBM); st != MXB200_OK)
     return st;
-  if (int st = make_operand_map(&mb, b, N, K, bn); st != MXB200_OK)
+  if (int st = make_operand_map(&mb, b, N, K, plan.tile_n); st != MXB200_OK)
     return st;
-  const int cap = g_max_ctas.load() > 0 ? g_max_ctas.load() : dev.sms;
   const int grid = static_cast<int>(std::min<int64_t>(tiles * p.splits, cap));
-  return bn == 256 ? launch<256>(ma, mb, p, grid, s) : launch<128>(ma, mb, p, grid, s);
+  return plan.tile_n == 256 ? launch<256>(ma, mb, p, grid, s) : launch<128>(ma, mb, p, grid, s);
 }
 
 }  // namespace
@@ -641,12 +1132,12 @@ extern "C" int mxb200_gemm_splits(int64_t M, int64_t N, int64_t K) {
   mxb200::DeviceInfo dev;
   if (mxb200::current_device(&dev) != MXB200_OK || M <= 0 || N <= 0 || K <= 0)
     return 1;
-  const int bn = mxb200::choose_bn(N);
-  const int64_t tiles = (M / 128) * ((N + bn - 1) / bn);
+  const mxb200::TilePlan plan = mxb200::plan_tiles(M, N, K, dev.sms);
+  const int64_t tiles = plan.tiles(), slots = plan.slots;
   const int64_t k_tiles = K / 128;
   // Splitting costs a round trip of fp32 partial tiles through the workspace, so it only pays when the tiles
   // alone cannot fill the machine for two waves and every slice keeps a deep main loop.
-  if (tiles >= 2 * dev.sms)
+  if (tiles >= 2 * slots)
     return 1;
   int best = 1;
   double best_score = 0.0;
@@ -654,8 +1145,8 @@ extern "C" int mxb200_gemm_splits(int64_t M, int64_t N, int64_t K) {
     if (s > 1 && k_tiles / s < 32)
       break;
     const int64_t units = tiles * s;
-    const int64_t waves = (units + dev.sms - 1) / dev.sms;
-    const double score = static_cast<double>(units) / static_cast<double>(waves * dev.sms) * (s == 1 ? 1.0 : 0.9);
+    const int64_t waves = (units + slots - 1) / slots;
+    const double score = static_cast<double>(units) / static_cast<double>(waves * slots) * (s == 1 ? 1.0 : 0.9);
     if (score > best_score + 1e-9) {
       best_score = score;
       best = s;
@@ -665,12 +1156,12 @@ extern "C" int mxb200_gemm_splits(int64_t M, int64_t N, int64_t K) {
 }
 
 extern "C" size_t mxb200_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int splits) {
-  (void)K;
-  if (splits <= 1 || M <= 0 || N <= 0)
+  mxb200::DeviceInfo dev;
+  if (splits <= 1 || M <= 0 || N <= 0 || K <= 0)
     return 0;
-  const int bn = mxb200::choose_bn(N);
-  const int64_t tiles = (M / 128) * ((N + bn - 1) / bn);
-  return mxb200::counters_bytes(tiles) + static_cast<size_t>(tiles) * splits * 128 * bn * sizeof(float);
+  if (mxb200::current_device(&dev) != MXB200_OK)
+    dev.sms = 148;
+  return mxb200::workspace_bytes_for(mxb200::plan_tiles(M, N, K, dev.sms), splits);
 }
 
 extern "C" int mxb200_gemm_splitk(const void* a, const void* a_scale, const void* b, const void* b_scale, void* d,
@@ -681,7 +1172,7 @@ extern "C" int mxb200_gemm_splitk(const void* a, const void* a_scale, const void
 }
 
 extern "C" int mxb200_set_gemm_config(int tile_n, int max_ctas) {
-  if ((tile_n != 0 && tile_n != 128 && tile_n != 256) || max_ctas < 0)
+  if ((tile_n != 0 && tile_n != 128 && tile_n != 256 && tile_n != 384 && tile_n != 512) || max_ctas < 0)
     return MXB200_ERR_ARGUMENT;
   mxb200::g_tile_n.store(tile_n);
   mxb200::g_max_ctas.store(max_ctas);
@@ -731,3 +1222,10 @@ extern "C" int mxb200_gemm_splitk_static(const void* a, const void* a_scale, con
   return mxb200::gemm(a, a_scale, b, b_scale, d, out_kind, resid, M, N, K, alpha, accumulate, splits, scratch,
                       MXB200_STATIC_SCRATCH_BYTES, stream);
 }
+
+#ifdef MXB200_TRACE
+extern "C" __attribute__((visibility("default"))) int mxb200_trace_read(unsigned long long* out, int n) {
+  cudaDeviceSynchronize();
+  return cudaMemcpyFromSymbol(out, mxb200::g_trace, sizeof(unsigned long long) * n) == cudaSuccess ? 0 : 1;
+}
+#endif

@@ -2,6 +2,12 @@
 // shared memory of the CTA that issued it), tensor memory (tcgen05.alloc/ld/cp), the 5th-generation
 // tensor-core MMA (tcgen05.mma kind::mxf8f6f4.block_scale) in its one-CTA and CTA-pair forms, and the
 // cluster plumbing a CTA pair needs (rank, remote mbarrier arrive, cluster barrier). Device-only.
+//
+// The wrappers that issue asynchronous work (loads, copies, MMAs, commits, expect_tx) take `pred`: the whole warp
+// executes the call converged and only the lane whose pred is non-zero (one elected lane) issues the instruction.
+// Keeping the issuing warp converged lets the compiler hold descriptors and addresses in uniform registers;
+// issuing from inside a divergent `if (lane == 0)` costs roughly twice the cycles per instruction, enough to make
+// a 128 x 256 x 32 MMA stream issue-bound.
 #pragma once
 
 #include <cstdint>
@@ -42,8 +48,10 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
-__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t pred, uint64_t* bar, uint32_t bytes) {
+  asm volatile("{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %2, 0;\n\t"
+               "@q mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n\t}\n" ::"r"(smem_u32(bar)), "r"(bytes), "r"(pred)
+               : "memory");
 }
 
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
@@ -67,18 +75,22 @@ __device__ __forceinline__ void fence_proxy_async_smem() {
 
 // 2-D tiled load global -> shared, completion on an mbarrier of this CTA. x is the innermost coordinate and
 // must make x * element size a multiple of 16 bytes.
-__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int32_t x, int32_t y) {
+__device__ __forceinline__ void tma_load_2d(uint32_t pred, void* smem_dst, const CUtensorMap* map, uint64_t* bar,
+                                            int32_t x, int32_t y) {
   asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-        ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y)
+        "{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %5, 0;\n\t"
+        "@q cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n\t}\n"
+        ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(pred)
         : "memory");
 }
 
 // Untiled bulk copy global -> shared: both addresses 16-byte aligned, bytes % 16 == 0.
-__device__ __forceinline__ void bulk_load(void* smem_dst, const void* gmem_src, uint32_t bytes, uint64_t* bar) {
+__device__ __forceinline__ void bulk_load(uint32_t pred, void* smem_dst, const void* gmem_src, uint32_t bytes,
+                                          uint64_t* bar) {
   asm volatile(
-        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-        ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(gmem_src)), "r"(bytes), "r"(smem_u32(bar))
+        "{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %4, 0;\n\t"
+        "@q cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n\t}\n"
+        ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(gmem_src)), "r"(bytes), "r"(smem_u32(bar)), "r"(pred)
         : "memory");
 }
 
@@ -133,25 +145,31 @@ __device__ __forceinline__ void tcgen05_fence_after_sync() {
 }
 
 // All tcgen05.mma / tcgen05.cp issued so far by this thread arrive on the mbarrier when they complete.
-__device__ __forceinline__ void tcgen05_commit(uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+__device__ __forceinline__ void tcgen05_commit(uint32_t pred, uint64_t* bar) {
+  asm volatile("{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %1, 0;\n\t"
+               "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}\n"
+               ::"r"(smem_u32(bar)), "r"(pred)
                : "memory");
 }
 
 // 32 rows x 16 bytes of shared memory (one 512-byte scale tile) -> TMEM lanes 0..31 x 4 columns, replicated
 // into all four 32-lane quarters.
-__device__ __forceinline__ void tcgen05_cp_32x128b_warpx4(uint32_t taddr, uint64_t smem_desc) {
-  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(smem_desc) : "memory");
+__device__ __forceinline__ void tcgen05_cp_32x128b_warpx4(uint32_t pred, uint32_t taddr, uint64_t smem_desc) {
+  asm volatile("{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %2, 0;\n\t"
+               "@q tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;\n\t}\n" ::"r"(taddr), "l"(smem_desc), "r"(pred)
+               : "memory");
 }
 
 // D[tmem] (+)= A[smem] . B[smem]^T with per-32 block scales from TMEM; one K = 32 step.
-__device__ __forceinline__ void tcgen05_mma_mxf8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                                 uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
+__device__ __forceinline__ void tcgen05_mma_mxf8(uint32_t pred, uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                                 uint32_t idesc, uint32_t sfa_tmem, uint32_t sfb_tmem,
+                                                 uint32_t accumulate) {
   asm volatile(
-        "{\n\t.reg .pred p;\n\t"
+        "{\n\t.reg .pred p, q;\n\t"
         "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}\n"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
+        "setp.ne.b32 q, %7, 0;\n\t"
+        "@q tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}\n"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem), "r"(pred)
         : "memory");
 }
 
@@ -222,27 +240,33 @@ __device__ __forceinline__ void cluster_wait() {
   asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
-// Arrive on an mbarrier anywhere in the cluster (address from map_to_cta).
+// Arrive on an mbarrier anywhere in the cluster (address from map_to_cta). Default semantics (release at CTA
+// scope): what travels through these barriers is tensor-memory state ordered by tcgen05 fences, not generic
+// memory, and a cluster-scope release would first wait for all of the thread's earlier writes to be visible
+// cluster-wide, which costs thousands of cycles behind a stream of output stores.
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 
 // Tiled loads for a CTA pair: data lands in the issuing CTA's shared memory, the byte count is credited to an
 // mbarrier that may live in the pair's other CTA (cluster address).
-__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* map, uint32_t bar_cluster_addr,
-                                                 int32_t x, int32_t y) {
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t pred, void* smem_dst, const CUtensorMap* map,
+                                                 uint32_t bar_cluster_addr, int32_t x, int32_t y) {
   asm volatile(
-        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-        ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster_addr), "r"(x), "r"(y)
+        "{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %5, 0;\n\t"
+        "@q cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n\t}\n"
+        ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster_addr), "r"(x), "r"(y), "r"(pred)
         : "memory");
 }
 
-__device__ __forceinline__ void tma_load_4d_pair(void* smem_dst, const CUtensorMap* map, uint32_t bar_cluster_addr,
-                                                 int32_t c0, int32_t c1, int32_t c2, int32_t c3) {
+__device__ __forceinline__ void tma_load_4d_pair(uint32_t pred, void* smem_dst, const CUtensorMap* map,
+                                                 uint32_t bar_cluster_addr, int32_t c0, int32_t c1, int32_t c2,
+                                                 int32_t c3) {
   asm volatile(
-        "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        "{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %7, 0;\n\t"
+        "@q cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];\n\t}\n"
         ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster_addr), "r"(c0), "r"(c1),
-        "r"(c2), "r"(c3)
+        "r"(c2), "r"(c3), "r"(pred)
         : "memory");
 }
 
@@ -261,26 +285,31 @@ __device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t cols)
 }
 
 // Completion of the pair's MMAs / copies so far arrives on the mbarrier at this offset in every CTA of cta_mask.
-__device__ __forceinline__ void tcgen05_commit_pair(uint64_t* bar, uint16_t cta_mask) {
-  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
-               ::"r"(smem_u32(bar)), "h"(cta_mask)
+__device__ __forceinline__ void tcgen05_commit_pair(uint32_t pred, uint64_t* bar, uint16_t cta_mask) {
+  asm volatile("{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %2, 0;\n\t"
+               "@q tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;\n\t}\n"
+               ::"r"(smem_u32(bar)), "h"(cta_mask), "r"(pred)
                : "memory");
 }
 
 // Each CTA of the pair copies the scale tile at this offset of its own shared memory into its own TMEM.
-__device__ __forceinline__ void tcgen05_cp_32x128b_warpx4_pair(uint32_t taddr, uint64_t smem_desc) {
-  asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(smem_desc) : "memory");
+__device__ __forceinline__ void tcgen05_cp_32x128b_warpx4_pair(uint32_t pred, uint32_t taddr, uint64_t smem_desc) {
+  asm volatile("{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %2, 0;\n\t"
+               "@q tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;\n\t}\n" ::"r"(taddr), "l"(smem_desc), "r"(pred)
+               : "memory");
 }
 
 // One K = 32 step of a 256-row MMA across the pair: each CTA supplies 128 rows of A and half of B's rows from
 // the same shared-memory offsets and accumulates its 128 rows of D in its own TMEM.
-__device__ __forceinline__ void tcgen05_mma_mxf8_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                                      uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
+__device__ __forceinline__ void tcgen05_mma_mxf8_pair(uint32_t pred, uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                                      uint32_t idesc, uint32_t sfa_tmem, uint32_t sfb_tmem,
+                                                      uint32_t accumulate) {
   asm volatile(
-        "{\n\t.reg .pred p;\n\t"
+        "{\n\t.reg .pred p, q;\n\t"
         "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}\n"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
+        "setp.ne.b32 q, %7, 0;\n\t"
+        "@q tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}\n"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem), "r"(pred)
         : "memory");
 }
 

@@ -45,7 +45,7 @@ def _default_config():
 
 
 @pytest.mark.parametrize("M,N,K", SHAPES)
-@pytest.mark.parametrize("tile_n", [128, 256])
+@pytest.mark.parametrize("tile_n", [128, 256, 384, 512])
 def test_bf16_and_f32_match_oracle(M, N, K, tile_n):
     nc.capi.lib.mxb200_set_gemm_config(tile_n, 0)
     qa, qb = quantized(M, N, K)
@@ -87,7 +87,7 @@ def test_f32_accumulate_with_device_alpha(M, N, K):
     assert rel(acc, 2 * once) < 1e-6
 
 
-@pytest.mark.parametrize("tile_n", [128, 256])
+@pytest.mark.parametrize("tile_n", [128, 256, 384, 512])
 def test_fused_residual_is_bit_exact_with_separate_add(tile_n):
     """bf16(float(bf16(acc)) + resid): the reference's separate x + r (residual_norm_kernel.cu:96-104)."""
     nc.capi.lib.mxb200_set_gemm_config(tile_n, 0)
@@ -106,21 +106,25 @@ def test_fused_residual_is_bit_exact_with_separate_add(tile_n):
     assert rel(fused.float().cpu(), torch.from_numpy(want)) < TOL_BF16
 
 
-@pytest.mark.parametrize("N", [384, 640])
-def test_partial_last_tile(N):
-    """N % 256 == 128: the last 256-wide tile is half empty."""
-    nc.capi.lib.mxb200_set_gemm_config(256, 0)
-    qa, qb = quantized(256, N, 512, seed=6)
+@pytest.mark.parametrize("M,N", [(256, 384), (256, 640), (384, 384), (640, 896), (128, 1024)])
+@pytest.mark.parametrize("tile_n", [256, 384, 512])
+def test_partial_last_tiles(M, N, tile_n):
+    """N % 256 == 128 (and, for the CTA-pair kernel, M % 256 == 128): the last tile is half empty."""
+    nc.capi.lib.mxb200_set_gemm_config(tile_n, 0)
+    qa, qb = quantized(M, N, 512, seed=6)
     want = oracle_product(qa, qb)
-    canary = torch.full((256 * N + 64,), float("nan"), device="cuda")
-    out = canary[: 256 * N].view(256, N)
+    canary = torch.full((M * N + 4096,), float("nan"), device="cuda")
+    out = canary[: M * N].view(M, N)
     nc.mx_gemm_out(out, qa.data, qa.inv_scale, qb.data, qb.inv_scale)
     assert rel(out.cpu(), want) < TOL_F32
-    assert torch.isnan(canary[256 * N:]).all(), "wrote past the output"
+    assert torch.isnan(canary[M * N:]).all(), "wrote past the output"
+    out16 = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    nc.mx_gemm_out(out16, qa.data, qa.inv_scale, qb.data, qb.inv_scale)
+    assert torch.equal(out16, out.to(torch.bfloat16))
 
 
 @pytest.mark.parametrize("splits", [2, 3, 4])
-@pytest.mark.parametrize("tile_n", [128, 256])
+@pytest.mark.parametrize("tile_n", [128, 256, 384, 512])
 def test_split_k_matches_single_pass_and_is_deterministic(splits, tile_n):
     """The weight-gradient shape class: long K, few tiles. Slices are summed in fixed order."""
     nc.capi.lib.mxb200_set_gemm_config(tile_n, 0)
