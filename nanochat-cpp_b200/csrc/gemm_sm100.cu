@@ -143,6 +143,30 @@ __device__ __forceinline__ bool wait_bounded_warp(uint64_t* bar, uint32_t parity
   return __all_sync(0xffffffffu, wait_bounded(bar, parity, bars, site)) != 0;
 }
 
+// ... and with the barrier given as a shared-memory address
+__device__ __forceinline__ bool wait_bounded_warp(uint32_t bar_addr, uint32_t parity, Barriers* bars, uint32_t site) {
+  bool ok = true;
+  if (!mbar_try_wait(bar_addr, parity)) {
+    const uint64_t t0 = global_timer_ns();
+    uint32_t spins = 0;
+    while (!mbar_try_wait(bar_addr, parity)) {
+      if ((++spins & 63u) == 0) {
+        if (*reinterpret_cast<volatile uint32_t*>(&bars->abort_flag) != 0) {
+          ok = false;
+          break;
+        }
+        if (global_timer_ns() - t0 > kWaitLimitNs) {
+          *reinterpret_cast<volatile uint32_t*>(&bars->abort_flag) = 1;
+          atomicCAS(&g_watchdog_word, 0u, 0x80000000u | (blockIdx.x << 8) | site);
+          ok = false;
+          break;
+        }
+      }
+    }
+  }
+  return __all_sync(0xffffffffu, ok) != 0;
+}
+
 struct TileCoord {
   int m, n, split, tile;
 };
@@ -557,10 +581,12 @@ __global__ void __launch_bounds__(kThreads, 1)
 // matrix read as zero scales (2^-127) against zero data instead of touching memory out of range.
 
 // TN = 256: the widest tile (least L2 traffic per flop); its two accumulator buffers overlap by 32 columns, so
-// the next tile's first MMA waits until the previous tile's epilogue has read those columns: a bubble of several
-// hundred cycles per tile, negligible for long K. TN = 192: two disjoint 192-column buffers, no bubble, for
-// shapes with a short main loop. Scale tiles of B are always loaded as the two 128-row tiles covering the tile's
-// columns; an odd 192-wide tile starts 64 rows into the first one, i.e. 2 TMEM columns in.
+// the next tile's first MMA waits until the previous tile's epilogue has read those columns: a bubble of about
+// 1500 cycles per tile, negligible for long K. TN = 192: two disjoint buffers, no bubble, for shapes with a
+// short main loop. Scale tiles of B are loaded as the two 128-row tiles covering the tile's columns; the tile's
+// first column is ((n * TN) % 128) / 32 TMEM columns into the first of them. That offset must be even: a scale
+// address at an odd column (a tile starting 32 or 96 rows into a scale tile, as a 224-wide tiling would) is a
+// misaligned-address fault, so tile widths are multiples of 64.
 constexpr int kEpiStageBytes = 2048;       // one epilogue warp's staging buffer for TMA stores
 constexpr int kPairThreads = 320;          // producer warp, MMA warp, 8 epilogue warps
 constexpr int kPairEpilogueThreads = 256;  // two warps per TMEM lane quarter, each half of the tile's columns
@@ -570,11 +596,12 @@ struct PairConfig {
   static_assert(TN == 192 || TN == 256, "tile width");
   static constexpr int kTileM = 256, kTileN = TN;
   static constexpr int kBRows = TN / 2;                // this CTA's rows of B
+  static constexpr int kSfbTiles = 2;
   static constexpr uint32_t kABytes = 128 * kBK;       // this CTA's 128 rows of A
   static constexpr uint32_t kBBytes = kBRows * kBK;
-  static constexpr uint32_t kSfBytes = kScaleTileBytes * 3;  // A: own 128 rows; B: two tiles
+  static constexpr uint32_t kSfBytes = kScaleTileBytes * (1 + kSfbTiles);  // A: own 128 rows; B: all its tiles
   static constexpr uint32_t kTxPerCta = kABytes + kBBytes + kSfBytes;
-  static constexpr int kStages = TN == 256 ? 6 : 7;
+  static constexpr int kStages = TN == 192 ? 7 : 6;
   static constexpr bool kOverlap = TN == 256;
   static constexpr uint32_t kAcc0 = 0, kAcc1 = kOverlap ? 224 : TN;
   static constexpr uint32_t kSfaCol = kOverlap ? 480 : 2 * TN, kSfbCol = kSfaCol + 4;
@@ -638,10 +665,15 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
 
   if (warp == 0) {
     // ------------------------------------------------------------------ producer (both CTAs; one lane issues)
+    // Shared-memory and barrier addresses advance by a constant per stage and wrap with the ring: the issuing
+    // warp's per-stage instruction count is what bounds the pipeline once the MMA stream is saturated.
     {
       const uint32_t el = elect_one() ? 1u : 0u;
-      int stage = 0;
-      uint32_t phase = 0;
+      const uint32_t el_leader = leader ? el : 0u;
+      const uint32_t a0 = smem_u32(s_a), b0 = smem_u32(s_b), sf0 = smem_u32(s_sf);
+      const uint32_t empty0 = smem_u32(&bars->empty[0]), full0 = smem_u32(&bars->full[0]);
+      const uint32_t full_leader0 = map_to_cta(full0, 0);
+      uint32_t stage = 0, phase = 0;
       bool ok = true;
       for (int unit = pair; ok && unit < total_units; unit += num_pairs) {
         const TileCoord tc = decode_unit(p, unit);
@@ -649,19 +681,20 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
         const int k_end = min(k_begin + p.k_tiles_split, p.k_tiles_total);
         const int row_a = tc.m * C::kTileM + static_cast<int>(rank) * 128;
         const int row_b = tc.n * C::kTileN + static_cast<int>(rank) * C::kBRows;
+        const int sfa_tile = row_a >> 7, sfb_tile = (tc.n * C::kTileN) >> 7;
         if (el) TRACE(4, (unit - pair) / num_pairs);
         for (int kt = k_begin; kt < k_end; ++kt) {
-          if (!wait_bounded_warp(&bars->empty[stage], phase ^ 1u, bars, kSiteProducerEmpty)) {
+          if (!wait_bounded_warp(empty0 + stage * 8, phase ^ 1u, bars, kSiteProducerEmpty)) {
             ok = false;
             break;
           }
-          mbar_arrive_expect_tx(leader ? el : 0u, &bars->full[stage], 2 * C::kTxPerCta);
-          const uint32_t full = map_to_cta(smem_u32(&bars->full[stage]), 0);
-          tma_load_2d_pair(el, s_a + stage * C::kABytes, &map_a, full, kt * kBK, row_a);
-          tma_load_2d_pair(el, s_b + stage * C::kBBytes, &map_b, full, kt * kBK, row_b);
-          unsigned char* sf = s_sf + stage * C::kSfBytes;
-          tma_load_4d_pair(el, sf, &map_sfa, full, 0, 0, kt, row_a >> 7);
-          tma_load_4d_pair(el, sf + kScaleTileBytes, &map_sfb, full, 0, 0, kt, (tc.n * C::kTileN) >> 7);
+          mbar_arrive_expect_tx(el_leader, full0 + stage * 8, 2 * C::kTxPerCta);
+          const uint32_t full = full_leader0 + stage * 8;
+          const uint32_t sf = sf0 + stage * C::kSfBytes;
+          tma_load_2d_pair(el, a0 + stage * C::kABytes, &map_a, full, kt * kBK, row_a);
+          tma_load_2d_pair(el, b0 + stage * C::kBBytes, &map_b, full, kt * kBK, row_b);
+          tma_load_4d_pair(el, sf, &map_sfa, full, 0, 0, kt, sfa_tile);
+          tma_load_4d_pair(el, sf + kScaleTileBytes, &map_sfb, full, 0, 0, kt, sfb_tile);
           if (++stage == C::kStages) {
             stage = 0;
             phase ^= 1u;
@@ -673,12 +706,17 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
     // ------------------------------------------------------------------ MMA issuer (leader CTA only)
     if (leader) {
       const uint32_t el = elect_one() ? 1u : 0u;
-      int stage = 0;
-      uint32_t phase = 0;
+      uint32_t stage = 0, phase = 0;
       uint32_t local = 0;
       bool ok = true;
       const uint32_t sfa_t = tmem_base + C::kSfaCol, sfb_t = tmem_base + C::kSfbCol;
       const uint32_t idesc = make_idesc_mxf8(C::kTileM, C::kTileN);
+      const uint32_t empty0 = smem_u32(&bars->empty[0]), full0 = smem_u32(&bars->full[0]);
+      // operand tiles: K-major, 128-byte swizzle, 8-row groups 1024 bytes apart; scale tiles: 32 rows x 16 bytes,
+      // 8-row groups 128 bytes apart, no swizzle
+      const uint64_t a_desc0 = make_smem_desc(smem_u32(s_a), 16, 1024, 2);
+      const uint64_t b_desc0 = make_smem_desc(smem_u32(s_b), 16, 1024, 2);
+      const uint64_t sf_desc0 = make_smem_desc(smem_u32(s_sf), 0, 128, 0);
       for (int unit = pair; ok && unit < total_units; unit += num_pairs, ++local) {
         const TileCoord tc = decode_unit(p, unit);
         const uint32_t buf = local & 1u, use = local >> 1;
@@ -699,22 +737,26 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
         const int k_begin = tc.split * p.k_tiles_split;
         const int k_end = min(k_begin + p.k_tiles_split, p.k_tiles_total);
         for (int kt = k_begin; kt < k_end; ++kt) {
-          if (!wait_bounded_warp(&bars->full[stage], phase, bars, kSiteMmaFull)) {
+          if (!wait_bounded_warp(full0 + stage * 8, phase, bars, kSiteMmaFull)) {
             ok = false;
             break;
           }
-          tcgen05_fence_after_sync();
-          const uint32_t sf_addr = smem_u32(s_sf + stage * C::kSfBytes);
-          tcgen05_cp_32x128b_warpx4_pair(el, sfa_t, make_smem_desc(sf_addr, 0, 128, 0));
-          tcgen05_cp_32x128b_warpx4_pair(el, sfb_t, make_smem_desc(sf_addr + kScaleTileBytes, 0, 128, 0));
-          tcgen05_cp_32x128b_warpx4_pair(el, sfb_t + 4, make_smem_desc(sf_addr + 2 * kScaleTileBytes, 0, 128, 0));
-          const uint64_t a_desc = make_smem_desc(smem_u32(s_a + stage * C::kABytes), 16, 1024, 2);
-          const uint64_t b_desc = make_smem_desc(smem_u32(s_b + stage * C::kBBytes), 16, 1024, 2);
+          // descriptors of this stage: the ring's first stage plus a constant per stage (16-byte units)
+          const uint64_t sf_desc = sf_desc0 + stage * (C::kSfBytes >> 4);
+          tcgen05_cp_32x128b_warpx4_pair(el, sfa_t, sf_desc);
 #pragma unroll
-          for (uint32_t k = 0; k < 4; ++k)
+          for (int j = 0; j < C::kSfbTiles; ++j)
+            tcgen05_cp_32x128b_warpx4_pair(el, sfb_t + 4 * j, sf_desc + (1 + j) * (kScaleTileBytes >> 4));
+          const uint64_t a_desc = a_desc0 + stage * (C::kABytes >> 4);
+          const uint64_t b_desc = b_desc0 + stage * (C::kBBytes >> 4);
+          // K = 32 per step: 32 bytes (2 units) further into the swizzle atom; scale byte k of the 32-bit column
+          tcgen05_mma_mxf8_pair(el, acc_t, a_desc, b_desc, idesc_with_sf(idesc, 0, 0), sfa_t, sfb_mma,
+                                kt > k_begin ? 1u : 0u);
+#pragma unroll
+          for (uint32_t k = 1; k < 4; ++k)
             tcgen05_mma_mxf8_pair(el, acc_t, a_desc + 2 * k, b_desc + 2 * k, idesc_with_sf(idesc, k, k), sfa_t, sfb_mma,
-                                  (kt > k_begin || k > 0) ? 1u : 0u);
-          tcgen05_commit_pair(el, &bars->empty[stage], 3);  // frees this stage in both CTAs
+                                  1u);
+          tcgen05_commit_pair(el, empty0 + stage * 8, 3);  // frees this stage in both CTAs
           if (++stage == C::kStages) {
             stage = 0;
             phase ^= 1u;
@@ -737,8 +779,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
     uint32_t local = 0, sync_phase = 0;
     bool ok = true;
     constexpr int kChunks = C::kTileN / 32;
-    constexpr int kMine = kChunks / 2;      // chunks per warp
-    constexpr int kHalf = 128 * C::kTileN;  // elements of one CTA's half tile
+    constexpr int kMine = (kChunks + 1) / 2;  // chunks of column half 0; half 1 takes the remaining kChunks - kMine
+    constexpr int kHalf = 128 * C::kTileN;    // elements of one CTA's half tile
+    const int n_mine = col_half == 0 ? kMine : kChunks - kMine;
     const uint32_t empty_leader[2] = {map_to_cta(smem_u32(&bars->tmem_empty[0]), 0),
                                       map_to_cta(smem_u32(&bars->tmem_empty[1]), 0)};
     const uint32_t overlap_leader = map_to_cta(smem_u32(&bars->overlap_free), 0);
@@ -772,12 +815,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
       tmem_ld_32x32b_x32(acc_t + chunk_of(0) * 32, r[0]);
 #pragma unroll
       for (int i = 0; i < kMine; ++i) {
+        if (i >= n_mine)
+          break;
         const int c = chunk_of(i);
         tmem_ld_wait();
-        if (threadIdx.x == 64 && i == 0) TRACE(5, local);
-        if (threadIdx.x == 64 && i == 1) TRACE(6, local);
-        if (threadIdx.x == 64 && i == 2) TRACE(7, local);
-        if (i + 1 < kMine)
+        if (i + 1 < n_mine)
           tmem_ld_32x32b_x32(acc_t + chunk_of(i + 1) * 32, r[(i + 1) & 1]);
         if (i == 0 && owns_shared) {
           tcgen05_fence_before_sync();
@@ -797,16 +839,13 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
           const bool issue = warp_row0 < p.M && col < p.N;
           uint32_t o[32];
           compute_chunk(p, alpha, row, col, reinterpret_cast<const float*>(r[i & 1]), valid, o);
-          if (threadIdx.x == 64 && i == 2) TRACE(8, local);
           store_rows_tma(&map_d, stage, lane, o, col, warp_row0, issue);
-          if (threadIdx.x == 64 && i == 2) TRACE(9, local);
           if (p.out_kind == kOutF32)
             store_rows_tma(&map_d, stage, lane, o + 16, col + 16, warp_row0, issue);
         }
       }
       tcgen05_fence_before_sync();
       __syncwarp();
-      if (threadIdx.x == 64) TRACE(10, local);
       if (lane == 0)
         mbar_arrive_cluster(empty_leader[buf]);
       if (threadIdx.x == 64) TRACE(3, local);
@@ -840,7 +879,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
           const float* tile_part = p.partials + (static_cast<int64_t>(tc.tile) * p.splits * 2 + rank) * kHalf +
                                    static_cast<int64_t>(quarter * 32 + lane) * C::kTileN;
 #pragma unroll 1
-          for (int c = col_half * kMine; c < (col_half + 1) * kMine; ++c) {
+          for (int c = col_half * kMine; c < col_half * kMine + n_mine; ++c) {
             if (col0 + c * 32 >= p.N)
               break;
             float acc[32];
@@ -976,10 +1015,38 @@ TilePlan plan_tiles(int64_t M, int64_t N, int64_t K, int sms) {
   TilePlan t{};
   if (forced == 512 || forced == 384 || (forced == 0 && M >= 256 && N >= 256)) {
     t.pair = true, t.tile_m = 256, t.slots = std::max(sms / 2, 1);
-    // a short main loop cannot hide the 256-wide tile's hand-over bubble; take 192 when it tiles N well
-    const int64_t n192 = (N + 191) / 192 * 192;
-    const bool narrow = K <= 4096 && n192 * 20 <= N * 21;
-    t.tile_n = forced == 512 ? 256 : (forced == 384 ? 192 : (narrow ? 192 : 256));
+    if (forced == 512) {
+      t.tile_n = 256;
+    } else if (forced == 384) {
+      t.tile_n = 192;
+    } else {
+      // Estimated cycles: waves x (main loop, execution- or issue-bound, + the hand-over between tiles), for the
+      // tile count including the K split the caller will choose. 256 pays an overlap bubble per tile.
+      const int64_t k_iters = K / 128;
+      double best = 0.0;
+      for (int tn : {256, 192}) {
+        const int64_t tiles = ((M + 255) / 256) * ((N + tn - 1) / tn);
+        int64_t units = tiles, iters = k_iters;
+        if (tiles < 2 * t.slots) {  // few tiles: the split-K heuristic will cut K, up to 4 ways
+          int s_best = 1;
+          double s_score = 0.0;
+          for (int sp = 1; sp <= 4; ++sp) {
+            if (sp > 1 && k_iters / sp < 32)
+              break;
+            const int64_t u = tiles * sp, w = (u + t.slots - 1) / t.slots;
+            const double sc = static_cast<double>(u) / static_cast<double>(w * t.slots) * (sp == 1 ? 1.0 : 0.9);
+            if (sc > s_score + 1e-9)
+              s_score = sc, s_best = sp;
+          }
+          units = tiles * s_best, iters = (k_iters + s_best - 1) / s_best;
+        }
+        const int64_t waves = (units + t.slots - 1) / t.slots;
+        const double per_tile = static_cast<double>(iters) * std::max(2 * tn, 400) + (tn == 256 ? 1500.0 : 300.0);
+        const double cost = static_cast<double>(waves) * per_tile;
+        if (best == 0.0 || cost < best * 0.995)
+          best = cost, t.tile_n = tn;
+      }
+    }
   } else {
     t.pair = false, t.tile_m = 128, t.slots = std::max(sms, 1);
     t.tile_n = (forced == 128 || forced == 256) ? forced : (N >= 256 ? 256 : 128);
@@ -1102,8 +1169,9 @@ int gemm(const void* a, const void* a_scale, const void* b, const void* b_scale,
     if (int st = make_scale_map(&msb, b_scale, N, K, 2); st != MXB200_OK)
       return st;
     const int pairs = static_cast<int>(std::min<int64_t>(tiles * p.splits, std::max(cap / 2, 1)));
-    return plan.tile_n == 256 ? launch_pair<256>(ma, mb, msa, msb, md, p, pairs, s)
-                              : launch_pair<192>(ma, mb, msa, msb, md, p, pairs, s);
+    if (plan.tile_n == 256)
+      return launch_pair<256>(ma, mb, msa, msb, md, p, pairs, s);
+    return launch_pair<192>(ma, mb, msa, msb, md, p, pairs, s);
   }
   if (int st = make_operand_map(&ma, a, M, K, kBM); st != MXB200_OK)
     return st;

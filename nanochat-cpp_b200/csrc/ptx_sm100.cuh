@@ -66,6 +66,25 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return done != 0;
 }
 
+// Overloads taking the barrier as a shared-memory address (the issuing warps keep running addresses).
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar_addr, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}\n"
+        : "=r"(done)
+        : "r"(bar_addr), "r"(parity)
+        : "memory");
+  return done != 0;
+}
+
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t pred, uint32_t bar_addr, uint32_t bytes) {
+  asm volatile("{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %2, 0;\n\t"
+               "@q mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n\t}\n" ::"r"(bar_addr), "r"(bytes), "r"(pred)
+               : "memory");
+}
+
 // Generic-proxy writes to shared memory made visible to the async proxy (TMA stores, tcgen05 reads).
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -250,22 +269,22 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
 
 // Tiled loads for a CTA pair: data lands in the issuing CTA's shared memory, the byte count is credited to an
 // mbarrier that may live in the pair's other CTA (cluster address).
-__device__ __forceinline__ void tma_load_2d_pair(uint32_t pred, void* smem_dst, const CUtensorMap* map,
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t pred, uint32_t smem_dst, const CUtensorMap* map,
                                                  uint32_t bar_cluster_addr, int32_t x, int32_t y) {
   asm volatile(
         "{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %5, 0;\n\t"
         "@q cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n\t}\n"
-        ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster_addr), "r"(x), "r"(y), "r"(pred)
+        ::"r"(smem_dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster_addr), "r"(x), "r"(y), "r"(pred)
         : "memory");
 }
 
-__device__ __forceinline__ void tma_load_4d_pair(uint32_t pred, void* smem_dst, const CUtensorMap* map,
+__device__ __forceinline__ void tma_load_4d_pair(uint32_t pred, uint32_t smem_dst, const CUtensorMap* map,
                                                  uint32_t bar_cluster_addr, int32_t c0, int32_t c1, int32_t c2,
                                                  int32_t c3) {
   asm volatile(
         "{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %7, 0;\n\t"
         "@q cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];\n\t}\n"
-        ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster_addr), "r"(c0), "r"(c1),
+        ::"r"(smem_dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster_addr), "r"(c0), "r"(c1),
         "r"(c2), "r"(c3), "r"(pred)
         : "memory");
 }
@@ -285,11 +304,15 @@ __device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t cols)
 }
 
 // Completion of the pair's MMAs / copies so far arrives on the mbarrier at this offset in every CTA of cta_mask.
-__device__ __forceinline__ void tcgen05_commit_pair(uint32_t pred, uint64_t* bar, uint16_t cta_mask) {
+__device__ __forceinline__ void tcgen05_commit_pair(uint32_t pred, uint32_t bar_addr, uint16_t cta_mask) {
   asm volatile("{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %2, 0;\n\t"
                "@q tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;\n\t}\n"
-               ::"r"(smem_u32(bar)), "h"(cta_mask), "r"(pred)
+               ::"r"(bar_addr), "h"(cta_mask), "r"(pred)
                : "memory");
+}
+
+__device__ __forceinline__ void tcgen05_commit_pair(uint32_t pred, uint64_t* bar, uint16_t cta_mask) {
+  tcgen05_commit_pair(pred, smem_u32(bar), cta_mask);
 }
 
 // Each CTA of the pair copies the scale tile at this offset of its own shared memory into its own TMEM.

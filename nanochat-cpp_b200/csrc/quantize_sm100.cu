@@ -3,10 +3,11 @@
 // (src/nanochat/model/fp8/fp8_kernel.cu:197-210, body mx_kernel.cuh:72-107); same bytes, different schedule.
 //
 // One CTA owns a 128 x 128 tile, which is exactly one 512-byte swizzled scale tile in each layout.
-//   row pass:    each thread loads 8 consecutive values with one 128-bit (bf16) or 256-bit (fp32) load, fully
-//                coalesced; the block maximum of 32 values is a 4-lane shuffle reduction; 8 E4M3 bytes leave
-//                with one 64-bit store (a warp writes 256 contiguous bytes). The loaded values are parked in
-//                shared memory in their input type (prologue values are bf16-exact).
+//   row pass:    each thread loads 16 consecutive values with 256-bit loads (one for bf16, two for fp32), fully
+//                coalesced; the block maximum of 32 values is a 2-lane shuffle (for plain bf16 input the
+//                per-thread maximum is taken on the packed 16-bit patterns); 16 E4M3 bytes leave with one
+//                128-bit store (a warp writes 512 contiguous bytes). The loaded values are parked in shared
+//                memory in their input type (prologue values are bf16-exact).
 //   column pass: each thread owns two adjacent columns x 32 rows, read from shared memory as packed pairs
 //                (a warp reads 128 contiguous bytes per row, conflict-free), needs no shuffle, and writes
 //                32 contiguous bytes of each transposed row with one 256-bit store (a full DRAM sector).
@@ -54,27 +55,6 @@ __device__ __forceinline__ float prologue(float v, float h) {
   }
 }
 
-__device__ __forceinline__ void unpack_bf16x8(const uint4& raw, float (&v)[8]) {
-  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-#pragma unroll
-  for (int k = 0; k < 4; ++k) {
-    v[2 * k] = __uint_as_float(w[k] << 16);
-    v[2 * k + 1] = __uint_as_float(w[k] & 0xffff0000u);
-  }
-}
-
-// wide: the address is 32-byte aligned (one 256-bit access); the interface only promises 16 bytes
-__device__ __forceinline__ void load_f32x8(const float* p, float (&v)[8], bool wide) {
-  if (wide) {
-    asm volatile("ld.global.nc.L1::no_allocate.v8.f32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
-                 : "=f"(v[0]), "=f"(v[1]), "=f"(v[2]), "=f"(v[3]), "=f"(v[4]), "=f"(v[5]), "=f"(v[6]), "=f"(v[7])
-                 : "l"(p));
-  } else {
-    const float4 a = __ldg(reinterpret_cast<const float4*>(p)), b = __ldg(reinterpret_cast<const float4*>(p) + 1);
-    v[0] = a.x, v[1] = a.y, v[2] = a.z, v[3] = a.w, v[4] = b.x, v[5] = b.y, v[6] = b.z, v[7] = b.w;
-  }
-}
-
 __device__ __forceinline__ uint4 load_u4_stream(const void* p) {
   uint4 r;
   asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
@@ -105,9 +85,37 @@ __device__ __forceinline__ uint32_t cvt_e4m3x4(float a, float b, float c, float 
   return cvt_e4m3x2(a, b) | (cvt_e4m3x2(c, d) << 16);
 }
 
+__device__ __forceinline__ uint32_t max_u16x2(uint32_t a, uint32_t b) {
+  uint32_t r;
+  asm("max.u16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+
+// bits of max |x| over 16 bf16 values (8 packed words), NaNs included as the largest patterns
+__device__ __forceinline__ uint32_t absmax_bits_bf16x16(const uint32_t (&w)[8]) {
+  uint32_t m = max_u16x2(w[0] & 0x7fff7fffu, w[1] & 0x7fff7fffu);
+#pragma unroll
+  for (int k = 2; k < 8; ++k)
+    m = max_u16x2(m, w[k] & 0x7fff7fffu);
+  return max(m & 0xffffu, m >> 16);
+}
+
+__device__ __forceinline__ void load_u32x8_stream(const void* p, uint32_t (&w)[8], bool wide) {
+  if (wide) {
+    asm volatile("ld.global.nc.L1::no_allocate.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]), "=r"(w[4]), "=r"(w[5]), "=r"(w[6]), "=r"(w[7])
+                 : "l"(p));
+  } else {
+    const uint4 a = load_u4_stream(p), b = load_u4_stream(static_cast<const unsigned char*>(p) + 16);
+    w[0] = a.x, w[1] = a.y, w[2] = a.z, w[3] = a.w, w[4] = b.x, w[5] = b.y, w[6] = b.z, w[7] = b.w;
+  }
+}
+
 // kIn32: fp32 input (parked as float), else bf16 (parked as bf16).
+// Row pass: a thread owns 16 consecutive values of a row (one 256-bit load of bf16), two lanes share a 32-value
+// block (one shuffle), 16 E4M3 bytes leave with one 128-bit store (512 contiguous bytes per warp).
 template <bool kIn32, int kPro>
-__global__ void __launch_bounds__(kThreads) mxb200_quantize_kernel(const QuantParams p) {
+__global__ void __launch_bounds__(kThreads, kIn32 ? 2 : (kPro == kReluSquareBwd ? 3 : 4)) mxb200_quantize_kernel(const QuantParams p) {
   using Park = typename std::conditional<kIn32, float, __nv_bfloat16>::type;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   Park* tile = reinterpret_cast<Park*>(smem_raw);                               // [128][128]
@@ -119,73 +127,104 @@ __global__ void __launch_bounds__(kThreads) mxb200_quantize_kernel(const QuantPa
   const int64_t row0 = static_cast<int64_t>(tile_r) * kTile, col0 = static_cast<int64_t>(tile_c) * kTile;
   const bool want_rows = p.out.data != nullptr, want_cols = p.out_t.data != nullptr;
 
-  // ---- row pass: 128 rows x 16 vectors of 8 values = 2048 vectors, 8 per thread
-  constexpr int kIters = kTile * (kTile / 8) / kThreads;
-  float v[kIters][8];
-  {
-    // all loads first: 8 independent 16/32-byte requests per thread in flight
-    uint4 raw[kIn32 ? 1 : kIters], rawh[kPro == kReluSquareBwd ? kIters : 1];
+  // ---- row pass: 128 rows x 8 vectors of 16 values = 1024 vectors, 4 per thread
+  constexpr int kIters = kTile * (kTile / 16) / kThreads;
+  constexpr int kWords = kIn32 ? 16 : 8;  // 32-bit words of input per 16 values
+  uint32_t raw[kIters][kWords];
+  uint32_t rawh[kPro == kReluSquareBwd ? kIters : 1][8];
+  // all loads first: 4 (bf16) or 8 (fp32) independent 32-byte requests per thread in flight
 #pragma unroll
-    for (int it = 0; it < kIters; ++it) {
-      const int q = it * kThreads + t, r = q >> 4, c = (q & 15) * 8;
-      const int64_t i = (row0 + r) * p.cols + col0 + c;
-      if constexpr (kIn32) {
-        load_f32x8(static_cast<const float*>(p.x) + i, v[it], p.wide_in);
-      } else {
-        raw[it] = load_u4_stream(static_cast<const __nv_bfloat16*>(p.x) + i);
-        if constexpr (kPro == kReluSquareBwd)
-          rawh[it] = load_u4_stream(static_cast<const __nv_bfloat16*>(p.h) + i);
-      }
-    }
-    if constexpr (!kIn32) {
+  for (int it = 0; it < kIters; ++it) {
+    const int q = it * kThreads + t, r = q >> 3, c = (q & 7) * 16;
+    const int64_t i = (row0 + r) * p.cols + col0 + c;
+    if constexpr (kIn32) {
+      uint32_t lo[8], hi[8];
+      load_u32x8_stream(static_cast<const float*>(p.x) + i, lo, p.wide_in);
+      load_u32x8_stream(static_cast<const float*>(p.x) + i + 8, hi, p.wide_in);
 #pragma unroll
-      for (int it = 0; it < kIters; ++it) {
-        unpack_bf16x8(raw[it], v[it]);
-        if constexpr (kPro == kReluSquareBwd) {
-          float hv[8];
-          unpack_bf16x8(rawh[it], hv);
-#pragma unroll
-          for (int k = 0; k < 8; ++k)
-            v[it][k] = prologue<kPro>(v[it][k], hv[k]);
-        } else if constexpr (kPro != kNone) {
-#pragma unroll
-          for (int k = 0; k < 8; ++k)
-            v[it][k] = prologue<kPro>(v[it][k], 0.f);
-        }
-      }
+      for (int k = 0; k < 8; ++k)
+        raw[it][k] = lo[k], raw[it][8 + k] = hi[k];
+    } else {
+      load_u32x8_stream(static_cast<const __nv_bfloat16*>(p.x) + i, raw[it], p.wide_in);
+      if constexpr (kPro == kReluSquareBwd)
+        load_u32x8_stream(static_cast<const __nv_bfloat16*>(p.h) + i, rawh[it], p.wide_in);
     }
   }
 #pragma unroll
   for (int it = 0; it < kIters; ++it) {
-    const int q = it * kThreads + t, r = q >> 4, c = (q & 15) * 8;
-    if (want_cols) {
-      if constexpr (kIn32) {
+    const int q = it * kThreads + t, r = q >> 3, c = (q & 7) * 16;
+    float v[16];
+    uint32_t m_bits;  // bits of this thread's max |v|
+    if constexpr (kIn32) {
+      float m = 0.f;
+#pragma unroll
+      for (int k = 0; k < 16; ++k) {
+        v[k] = __uint_as_float(raw[it][k]);
+        m = fmaxf(m, fabsf(v[k]));  // fmaxf drops NaN, as the reference's amax
+      }
+      m_bits = __float_as_uint(m);
+      if (want_cols) {
         float4* dst = reinterpret_cast<float4*>(tile + r * kTile + c);
-        dst[0] = make_float4(v[it][0], v[it][1], v[it][2], v[it][3]);
-        dst[1] = make_float4(v[it][4], v[it][5], v[it][6], v[it][7]);
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          dst[k] = make_float4(v[4 * k], v[4 * k + 1], v[4 * k + 2], v[4 * k + 3]);
+      }
+    } else {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        v[2 * k] = __uint_as_float(raw[it][k] << 16);
+        v[2 * k + 1] = __uint_as_float(raw[it][k] & 0xffff0000u);
+      }
+      if constexpr (kPro == kNone) {
+        // integer order of |bf16| patterns is float order; a NaN pattern shows up as the maximum and sends the
+        // whole warp through the float path, which skips NaNs as fmaxf does
+        m_bits = absmax_bits_bf16x16(raw[it]) << 16;
+        if (__any_sync(0xffffffffu, m_bits > 0x7f800000u)) {
+          float m = 0.f;
+#pragma unroll
+          for (int k = 0; k < 16; ++k)
+            m = fmaxf(m, fabsf(v[k]));
+          m_bits = __float_as_uint(m);
+        }
+        if (want_cols) {
+          uint4* dst = reinterpret_cast<uint4*>(tile + r * kTile + c);
+          dst[0] = make_uint4(raw[it][0], raw[it][1], raw[it][2], raw[it][3]);
+          dst[1] = make_uint4(raw[it][4], raw[it][5], raw[it][6], raw[it][7]);
+        }
       } else {
-        uint4 pk;
-        pk.x = (__float_as_uint(v[it][0]) >> 16) | (__float_as_uint(v[it][1]) & 0xffff0000u);
-        pk.y = (__float_as_uint(v[it][2]) >> 16) | (__float_as_uint(v[it][3]) & 0xffff0000u);
-        pk.z = (__float_as_uint(v[it][4]) >> 16) | (__float_as_uint(v[it][5]) & 0xffff0000u);
-        pk.w = (__float_as_uint(v[it][6]) >> 16) | (__float_as_uint(v[it][7]) & 0xffff0000u);
-        *reinterpret_cast<uint4*>(tile + r * kTile + c) = pk;
+        float m = 0.f;
+        uint32_t pk[8];
+#pragma unroll
+        for (int k = 0; k < 16; ++k) {
+          float hv = 0.f;
+          if constexpr (kPro == kReluSquareBwd)
+            hv = (k & 1) ? __uint_as_float(rawh[it][k >> 1] & 0xffff0000u) : __uint_as_float(rawh[it][k >> 1] << 16);
+          v[k] = prologue<kPro>(v[k], hv);
+          m = fmaxf(m, fabsf(v[k]));
+        }
+        m_bits = __float_as_uint(m);
+#pragma unroll
+        for (int k = 0; k < 8; ++k)  // prologue values are bf16-exact: repack by truncation
+          pk[k] = (__float_as_uint(v[2 * k]) >> 16) | (__float_as_uint(v[2 * k + 1]) & 0xffff0000u);
+        if (want_cols) {
+          uint4* dst = reinterpret_cast<uint4*>(tile + r * kTile + c);
+          dst[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+          dst[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+        }
       }
     }
     if (want_rows) {
-      float m = 0.f;
-#pragma unroll
-      for (int k = 0; k < 8; ++k)
-        m = fmaxf(m, fabsf(v[it][k]));  // fmaxf drops NaN, as the reference's amax
-      m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
-      m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
-      const int e = mx_exponent(__float_as_uint(m), p.floor_rule);
+      // non-negative float bits order as integers
+      m_bits = max(m_bits, __shfl_xor_sync(0xffffffffu, m_bits, 1));
+      const int e = mx_exponent(m_bits, p.floor_rule);
       const float mul = __uint_as_float(mx_multiplier_bits(e));
-      uint2 o;
-      o.x = cvt_e4m3x4(v[it][0] * mul, v[it][1] * mul, v[it][2] * mul, v[it][3] * mul);
-      o.y = cvt_e4m3x4(v[it][4] * mul, v[it][5] * mul, v[it][6] * mul, v[it][7] * mul);
-      *reinterpret_cast<uint2*>(static_cast<unsigned char*>(p.out.data) + (row0 + r) * p.out.ld + col0 + c) = o;
-      if ((t & 3) == 0)
+      uint4 o;
+      o.x = cvt_e4m3x4(v[0] * mul, v[1] * mul, v[2] * mul, v[3] * mul);
+      o.y = cvt_e4m3x4(v[4] * mul, v[5] * mul, v[6] * mul, v[7] * mul);
+      o.z = cvt_e4m3x4(v[8] * mul, v[9] * mul, v[10] * mul, v[11] * mul);
+      o.w = cvt_e4m3x4(v[12] * mul, v[13] * mul, v[14] * mul, v[15] * mul);
+      *reinterpret_cast<uint4*>(static_cast<unsigned char*>(p.out.data) + (row0 + r) * p.out.ld + col0 + c) = o;
+      if ((t & 1) == 0)
         sc_rows[mx_scale_tile_offset(r, c >> 5)] = static_cast<unsigned char>(e);
     }
   }
@@ -194,28 +233,56 @@ __global__ void __launch_bounds__(kThreads) mxb200_quantize_kernel(const QuantPa
   // ---- column pass: thread = (column pair, 32-row block)
   if (want_cols) {
     const int cp = t & 63, rb = t >> 6;
-    float lo[32], hi[32];
-    float mlo = 0.f, mhi = 0.f;
-#pragma unroll
-    for (int k = 0; k < 32; ++k) {
-      const Park* src = tile + (rb * 32 + k) * kTile + 2 * cp;
-      if constexpr (kIn32) {
-        const float2 f = *reinterpret_cast<const float2*>(src);
-        lo[k] = f.x, hi[k] = f.y;
-      } else {
-        const uint32_t w = *reinterpret_cast<const uint32_t*>(src);
-        lo[k] = __uint_as_float(w << 16), hi[k] = __uint_as_float(w & 0xffff0000u);
-      }
-      mlo = fmaxf(mlo, fabsf(lo[k]));
-      mhi = fmaxf(mhi, fabsf(hi[k]));
-    }
-    const int elo = mx_exponent(__float_as_uint(mlo), p.floor_rule), ehi = mx_exponent(__float_as_uint(mhi), p.floor_rule);
-    const float mullo = __uint_as_float(mx_multiplier_bits(elo)), mulhi = __uint_as_float(mx_multiplier_bits(ehi));
     uint32_t wlo[8], whi[8];
+    int elo, ehi;
+    if constexpr (kIn32) {
+      float lo[32], hi[32];
+      float mlo = 0.f, mhi = 0.f;
 #pragma unroll
-    for (int k = 0; k < 8; ++k) {
-      wlo[k] = cvt_e4m3x4(lo[4 * k] * mullo, lo[4 * k + 1] * mullo, lo[4 * k + 2] * mullo, lo[4 * k + 3] * mullo);
-      whi[k] = cvt_e4m3x4(hi[4 * k] * mulhi, hi[4 * k + 1] * mulhi, hi[4 * k + 2] * mulhi, hi[4 * k + 3] * mulhi);
+      for (int k = 0; k < 32; ++k) {
+        const float2 f = *reinterpret_cast<const float2*>(tile + (rb * 32 + k) * kTile + 2 * cp);
+        lo[k] = f.x, hi[k] = f.y;
+        mlo = fmaxf(mlo, fabsf(lo[k]));
+        mhi = fmaxf(mhi, fabsf(hi[k]));
+      }
+      elo = mx_exponent(__float_as_uint(mlo), p.floor_rule), ehi = mx_exponent(__float_as_uint(mhi), p.floor_rule);
+      const float mullo = __uint_as_float(mx_multiplier_bits(elo)), mulhi = __uint_as_float(mx_multiplier_bits(ehi));
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        wlo[k] = cvt_e4m3x4(lo[4 * k] * mullo, lo[4 * k + 1] * mullo, lo[4 * k + 2] * mullo, lo[4 * k + 3] * mullo);
+        whi[k] = cvt_e4m3x4(hi[4 * k] * mulhi, hi[4 * k + 1] * mulhi, hi[4 * k + 2] * mulhi, hi[4 * k + 3] * mulhi);
+      }
+    } else {
+      // the two columns stay packed as bf16 pairs: 32 registers instead of 64, absmax on the 16-bit patterns
+      uint32_t w[32];
+#pragma unroll
+      for (int k = 0; k < 32; ++k)
+        w[k] = *reinterpret_cast<const uint32_t*>(tile + (rb * 32 + k) * kTile + 2 * cp);
+      uint32_t m = w[0] & 0x7fff7fffu;
+#pragma unroll
+      for (int k = 1; k < 32; ++k)
+        m = max_u16x2(m, w[k] & 0x7fff7fffu);
+      uint32_t blo = (m & 0xffffu) << 16, bhi = m & 0xffff0000u;
+      if (__any_sync(0xffffffffu, blo > 0x7f800000u || bhi > 0x7f800000u)) {  // a NaN somewhere: skip NaNs as fmaxf
+        float mlo = 0.f, mhi = 0.f;
+#pragma unroll
+        for (int k = 0; k < 32; ++k) {
+          mlo = fmaxf(mlo, fabsf(__uint_as_float(w[k] << 16)));
+          mhi = fmaxf(mhi, fabsf(__uint_as_float(w[k] & 0xffff0000u)));
+        }
+        blo = __float_as_uint(mlo), bhi = __float_as_uint(mhi);
+      }
+      elo = mx_exponent(blo, p.floor_rule), ehi = mx_exponent(bhi, p.floor_rule);
+      const float mullo = __uint_as_float(mx_multiplier_bits(elo)), mulhi = __uint_as_float(mx_multiplier_bits(ehi));
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        wlo[k] = cvt_e4m3x4(__uint_as_float(w[4 * k] << 16) * mullo, __uint_as_float(w[4 * k + 1] << 16) * mullo,
+                            __uint_as_float(w[4 * k + 2] << 16) * mullo, __uint_as_float(w[4 * k + 3] << 16) * mullo);
+        whi[k] = cvt_e4m3x4(__uint_as_float(w[4 * k] & 0xffff0000u) * mulhi,
+                            __uint_as_float(w[4 * k + 1] & 0xffff0000u) * mulhi,
+                            __uint_as_float(w[4 * k + 2] & 0xffff0000u) * mulhi,
+                            __uint_as_float(w[4 * k + 3] & 0xffff0000u) * mulhi);
+      }
     }
     unsigned char* dst = static_cast<unsigned char*>(p.out_t.data) + (col0 + 2 * cp) * p.out_t.ld + row0 + rb * 32;
     store_u32x8(dst, wlo, p.wide_out_t);
