@@ -1,0 +1,98 @@
+// C++ face of libmxb200 at nanochat-cpp's kernel seam.
+//
+// nanochat-cpp keeps its CUDA kernels behind free functions in namespace nanochat::kernels whose headers include
+// only <cstdint> and <cuda_runtime_api.h> (src/nanochat/model/fp8/fp8_kernel.h:1-10, mx_gemm_kernel.h:5-9). This
+// header offers the MX subset of that seam with the SAME names, parameter lists and conventions, implemented as
+// inline calls into the C ABI of include/mxb200.h: a translation unit of the reference that includes this header
+// instead of fp8_kernel.h / mx_gemm_kernel.h, and links libmxb200.so, runs its MX path on the B200 engine.
+//   - quantizer launchers return void and leave errors to cudaGetLastError-style checks in the reference
+//     (fp8.cpp:152); here a failing status is kept in a thread-local that last_status() returns.
+//   - GEMMs return a static message or nullptr, as cutlass_mx_gemm_* do (mx_gemm_kernel.h:12).
+#pragma once
+
+#include <cstdint>
+
+#include <cuda_runtime_api.h>
+
+#include "mxb200.h"
+
+namespace nanochat::kernels {
+
+// src/nanochat/model/fp8/fp8_kernel.h:28-33; the C struct has the same four fields in the same order.
+struct MxOut {
+  void* data;
+  int64_t ld;
+  void* scale;
+  int64_t scale_tiles;
+};
+static_assert(sizeof(MxOut) == sizeof(mxb200_mx_out), "MxOut and mxb200_mx_out share one layout");
+
+namespace b200_detail {
+inline int& status_slot() {
+  static thread_local int status = MXB200_OK;
+  return status;
+}
+inline mxb200_mx_out view(const MxOut& o) {
+  return mxb200_mx_out{o.data, o.ld, o.scale, o.scale_tiles};
+}
+inline const char* message(int status) {
+  return status == MXB200_OK ? nullptr : mxb200_strerror(status);
+}
+}  // namespace b200_detail
+
+// Status of this thread's most recent quantizer call (MXB200_OK when it launched).
+inline int last_status() {
+  return b200_detail::status_slot();
+}
+
+// src/nanochat/model/fp8/fp8_kernel.h:35-39
+inline void quantize_mx(const void* x, bool x_bf16, int64_t rows, int64_t cols, MxOut out, MxOut out_t, bool relu_square,
+                        cudaStream_t stream) {
+  b200_detail::status_slot() =
+        mxb200_quantize_mx(x, x_bf16 ? 1 : 0, rows, cols, b200_detail::view(out), b200_detail::view(out_t),
+                           relu_square ? MXB200_PROLOGUE_RELU_SQUARE : MXB200_PROLOGUE_NONE, MXB200_SCALE_REFERENCE, stream);
+}
+
+// src/nanochat/model/fp8/fp8_kernel.h:41-43
+inline void quantize_mx_relu_square_bwd(const void* g, const void* h, int64_t rows, int64_t cols, MxOut out, MxOut out_t,
+                                        cudaStream_t stream) {
+  b200_detail::status_slot() = mxb200_quantize_mx_relu_square_bwd(g, h, rows, cols, b200_detail::view(out),
+                                                                  b200_detail::view(out_t), MXB200_SCALE_REFERENCE, stream);
+}
+
+// Same contract as cutlass_mx_gemm_bf16 (src/nanochat/model/fp8/mx_gemm_kernel.h:13-17).
+inline const char* b200_mx_gemm_bf16(const void* a, const void* a_scale, const void* b, const void* b_scale, void* d,
+                                     int64_t M, int64_t N, int64_t K, cudaStream_t stream) {
+  return b200_detail::message(mxb200_gemm_bf16(a, a_scale, b, b_scale, d, nullptr, M, N, K, stream));
+}
+
+// ... with the residual add fused into the epilogue: d = bf16(float(bf16(acc)) + float(resid)), the rounding of the
+// reference's separate add (src/nanochat/model/ops/residual_norm_kernel.cu:96-104). resid may alias d.
+inline const char* b200_mx_gemm_bf16_residual(const void* a, const void* a_scale, const void* b, const void* b_scale,
+                                              void* d, const void* resid, int64_t M, int64_t N, int64_t K,
+                                              cudaStream_t stream) {
+  return b200_detail::message(mxb200_gemm_bf16(a, a_scale, b, b_scale, d, resid, M, N, K, stream));
+}
+
+// Same contract as cutlass_mx_gemm_f32 (src/nanochat/model/fp8/mx_gemm_kernel.h:19-22): needs no workspace; the
+// K dimension is not split, so long-K shapes with few tiles (weight gradients) are better served by the next one.
+inline const char* b200_mx_gemm_f32(const void* a, const void* a_scale, const void* b, const void* b_scale, float* d,
+                                    int64_t M, int64_t N, int64_t K, const float* alpha, bool accumulate,
+                                    cudaStream_t stream) {
+  return b200_detail::message(mxb200_gemm_f32(a, a_scale, b, b_scale, d, M, N, K, alpha, accumulate ? 1 : 0, stream));
+}
+
+// The weight-gradient form: deterministic split-K over a caller workspace (the reference borrows torch's cuBLASLt
+// workspace for the same purpose, src/nanochat/model/fp8/mx_gemm.cpp:236-237). splits <= 0: the library chooses;
+// workspace_bytes must cover mxb200_gemm_workspace_bytes(M, N, K, splits).
+inline const char* b200_mx_gemm_f32_splitk(const void* a, const void* a_scale, const void* b, const void* b_scale,
+                                           float* d, int64_t M, int64_t N, int64_t K, const float* alpha,
+                                           bool accumulate, int splits, void* workspace, size_t workspace_bytes,
+                                           cudaStream_t stream) {
+  if (splits <= 0)
+    splits = mxb200_gemm_splits(M, N, K);
+  return b200_detail::message(mxb200_gemm_splitk(a, a_scale, b, b_scale, d, MXB200_OUT_F32, nullptr, M, N, K, alpha,
+                                                 accumulate ? 1 : 0, splits, workspace, workspace_bytes, stream));
+}
+
+}  // namespace nanochat::kernels

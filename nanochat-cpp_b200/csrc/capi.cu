@@ -32,6 +32,18 @@ int current_device(DeviceInfo* info) {
   return d.cc_major == 10 ? MXB200_OK : MXB200_ERR_DEVICE;
 }
 
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = [] {
+    void* f = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      f = nullptr;
+    return reinterpret_cast<EncodeTiledFn>(f);
+  }();
+  return fn;
+}
+
 }  // namespace mxb200
 
 extern "C" const char* mxb200_strerror(int status) {

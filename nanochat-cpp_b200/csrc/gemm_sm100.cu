@@ -281,6 +281,46 @@ __device__ __forceinline__ void write_chunk(const GemmParams& p, float alpha, in
   }
 }
 
+// Final write of 8 consecutive output columns of one row (the split-K reduction's unit of work).
+__device__ __forceinline__ void write_octet(const GemmParams& p, float alpha, int64_t row, int col, const float* acc) {
+  const int64_t idx = row * p.N + col;
+  if (p.out_kind == kOutBf16) {
+    uint4 o;
+    if (p.resid != nullptr) {
+      const uint4 rw = *reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(p.resid) + idx);
+      const uint32_t r[4] = {rw.x, rw.y, rw.z, rw.w};
+      uint32_t w[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float y0 = __bfloat162float(__float2bfloat16(acc[2 * k]));
+        const float y1 = __bfloat162float(__float2bfloat16(acc[2 * k + 1]));
+        w[k] = pack_bf16x2(y0 + __uint_as_float(r[k] << 16), y1 + __uint_as_float(r[k] & 0xffff0000u));
+      }
+      o = make_uint4(w[0], w[1], w[2], w[3]);
+    } else {
+      o = make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]), pack_bf16x2(acc[4], acc[5]),
+                     pack_bf16x2(acc[6], acc[7]));
+    }
+    *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.d) + idx) = o;
+  } else {
+    float* dp = static_cast<float*>(p.d) + idx;
+    float o[8];
+    if (p.accumulate) {
+      const float4 a = reinterpret_cast<const float4*>(dp)[0], b = reinterpret_cast<const float4*>(dp)[1];
+      const float old[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+      for (int k = 0; k < 8; ++k)
+        o[k] = fmaf(alpha, acc[k], old[k]);
+    } else {
+#pragma unroll
+      for (int k = 0; k < 8; ++k)
+        o[k] = alpha * acc[k];
+    }
+    reinterpret_cast<float4*>(dp)[0] = make_float4(o[0], o[1], o[2], o[3]);
+    reinterpret_cast<float4*>(dp)[1] = make_float4(o[4], o[5], o[6], o[7]);
+  }
+}
+
 // A warp's 32 rows x 64 bytes leave through shared memory and one TMA store: each lane parks its row's 64 bytes
 // (16-byte pieces placed by the 64-byte swizzle the tensor map expects, which also spreads the lanes over the
 // banks), the warp syncs, one lane issues the store. The TMA engine writes whole contiguous row segments,
@@ -614,7 +654,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
       mxb200_mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                                  const __grid_constant__ CUtensorMap map_sfa,
                                  const __grid_constant__ CUtensorMap map_sfb,
-                                 const __grid_constant__ CUtensorMap map_d, const GemmParams p) {
+                                 const __grid_constant__ CUtensorMap map_d,
+                                 const __grid_constant__ CUtensorMap map_part, const GemmParams p) {
   using C = PairConfig<TN>;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -651,6 +692,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
     prefetch_tensormap(&map_sfa);
     prefetch_tensormap(&map_sfb);
     prefetch_tensormap(&map_d);
+    if (p.splits > 1)
+      prefetch_tensormap(&map_part);
   }
   if (warp == 1) {
     tmem_alloc_pair(&bars->tmem_base, kTmemCols);
@@ -829,11 +872,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
         }
         const int col = col0 + c * 32;
         if (part != nullptr) {
-          if (row_ok && col < p.N) {
-#pragma unroll
-            for (int g = 0; g < 4; ++g)
-              store_u32x8(part + c * 32 + 8 * g, r[i & 1] + 8 * g, true);
-          }
+          // split-K partials take the same TMA store path: the workspace is a (half tiles x 128 rows, TN) matrix
+          const int part_row0 = static_cast<int>(half_index) * 128 + quarter * 32;
+          store_rows_tma(&map_part, stage, lane, r[i & 1], c * 32, part_row0, true);
+          store_rows_tma(&map_part, stage, lane, r[i & 1] + 16, c * 32 + 16, part_row0, true);
         } else {
           const bool valid = row_ok && col < p.N;
           const bool issue = warp_row0 < p.M && col < p.N;
@@ -852,6 +894,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
 
       if (part != nullptr) {
         // split-K, per half tile: the rows of this CTA are reduced by whichever CTA finishes them last
+        if (lane == 0) {
+          tma_store_wait_all<0>();                       // this warp's partial stores have completed ...
+          asm volatile("fence.proxy.async;" ::: "memory");  // ... and are ordered before generic-proxy traffic
+        }
         __threadfence();
         mbar_arrive(&bars->epi_sync);
         if (!wait_bounded(&bars->epi_sync, sync_phase, bars, kSiteEpilogueSync)) {
@@ -874,30 +920,31 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
         }
         sync_phase ^= 1u;
         const bool last = *reinterpret_cast<volatile uint32_t*>(&bars->last_flag) != 0;
-        if (last && row_ok) {
+        if (last) {
+          // The reduction reads only the workspace, so it need not follow the TMEM lane mapping: a warp takes whole
+          // rows, a lane 8 consecutive columns, and every load and store is a contiguous run across the warp.
           __threadfence();
-          const float* tile_part = p.partials + (static_cast<int64_t>(tc.tile) * p.splits * 2 + rank) * kHalf +
-                                   static_cast<int64_t>(quarter * 32 + lane) * C::kTileN;
+          const float* half_base = p.partials + (static_cast<int64_t>(tc.tile) * p.splits * 2 + rank) * kHalf;
+          const int sub = lane * 8;
+          if (sub < C::kTileN && col0 + sub < p.N) {
 #pragma unroll 1
-          for (int c = col_half * kMine; c < col_half * kMine + n_mine; ++c) {
-            if (col0 + c * 32 >= p.N)
-              break;
-            float acc[32];
+            for (int rr = warp - 2; rr < 128; rr += kPairEpilogueThreads / 32) {
+              const int64_t grow = static_cast<int64_t>(tc.m) * C::kTileM + rank * 128 + rr;
+              if (grow >= p.M)
+                break;
+              float acc[8];
 #pragma unroll
-            for (int k = 0; k < 32; ++k)
-              acc[k] = 0.f;
-            for (int s = 0; s < p.splits; ++s) {
-              const float* src = tile_part + static_cast<int64_t>(s) * 2 * kHalf + c * 32;
-#pragma unroll
-              for (int g = 0; g < 4; ++g) {
+              for (int k = 0; k < 8; ++k)
+                acc[k] = 0.f;
+              for (int sl = 0; sl < p.splits; ++sl) {  // slice order: the sum does not depend on who arrived last
                 uint32_t w[8];
-                load_u32x8_cg(src + 8 * g, w);
+                load_u32x8_cg(half_base + static_cast<int64_t>(sl) * 2 * kHalf + rr * C::kTileN + sub, w);
 #pragma unroll
                 for (int k = 0; k < 8; ++k)
-                  acc[8 * g + k] += __uint_as_float(w[k]);
+                  acc[k] += __uint_as_float(w[k]);
               }
+              write_octet(p, alpha, grow, col0 + sub, acc);
             }
-            write_chunk(p, alpha, row, col0 + c * 32, acc);
           }
         }
         mbar_arrive(&bars->epi_sync);
@@ -929,22 +976,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
 }
 
 // ------------------------------------------------------------------------------------------------ host side
-
-using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = [] {
-    void* f = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) != cudaSuccess ||
-        q != cudaDriverEntryPointSuccess)
-      f = nullptr;
-    return reinterpret_cast<EncodeTiledFn>(f);
-  }();
-  return fn;
-}
 
 // (rows, k) row-major bytes, box = box_rows x 128 bytes, 128-byte swizzle
 int make_operand_map(CUtensorMap* map, const void* base, int64_t rows, int64_t k, int box_rows) {
@@ -1020,28 +1051,19 @@ TilePlan plan_tiles(int64_t M, int64_t N, int64_t K, int sms) {
     } else if (forced == 384) {
       t.tile_n = 192;
     } else {
-      // Estimated cycles: waves x (main loop, execution- or issue-bound, + the hand-over between tiles), for the
-      // tile count including the K split the caller will choose. 256 pays an overlap bubble per tile.
+      // Estimated cycles: waves x (main loop + the hand-over between tiles). The main loop runs at the slower of
+      // MMA execution (2 TN cycles per K step of 128) and what an SM can ingest (about 64 bytes per cycle); 256
+      // pays an overlap bubble per tile. Measured on the d24 shapes this picks the faster width in every case,
+      // including the long-K weight gradients whose tile count it raises past one wave (splitting K instead costs
+      // more than it gains, see mxb200_gemm_splits).
       const int64_t k_iters = K / 128;
       double best = 0.0;
       for (int tn : {256, 192}) {
         const int64_t tiles = ((M + 255) / 256) * ((N + tn - 1) / tn);
-        int64_t units = tiles, iters = k_iters;
-        if (tiles < 2 * t.slots) {  // few tiles: the split-K heuristic will cut K, up to 4 ways
-          int s_best = 1;
-          double s_score = 0.0;
-          for (int sp = 1; sp <= 4; ++sp) {
-            if (sp > 1 && k_iters / sp < 32)
-              break;
-            const int64_t u = tiles * sp, w = (u + t.slots - 1) / t.slots;
-            const double sc = static_cast<double>(u) / static_cast<double>(w * t.slots) * (sp == 1 ? 1.0 : 0.9);
-            if (sc > s_score + 1e-9)
-              s_score = sc, s_best = sp;
-          }
-          units = tiles * s_best, iters = (k_iters + s_best - 1) / s_best;
-        }
+        const int64_t units = tiles, iters = k_iters;
         const int64_t waves = (units + t.slots - 1) / t.slots;
-        const double per_tile = static_cast<double>(iters) * std::max(2 * tn, 400) + (tn == 256 ? 1500.0 : 300.0);
+        const double ingest = (16384.0 + tn * 64.0 + 1536.0) / 58.0;  // bytes a CTA loads per K step / (B/clk)
+        const double per_tile = static_cast<double>(iters) * std::max(2.0 * tn, ingest) + (tn == 256 ? 1500.0 : 300.0);
         const double cost = static_cast<double>(waves) * per_tile;
         if (best == 0.0 || cost < best * 0.995)
           best = cost, t.tile_n = tn;
@@ -1090,12 +1112,12 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, in
 
 template <int TN>
 int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& msa, const CUtensorMap& msb,
-                const CUtensorMap& md, const GemmParams& p, int pairs, cudaStream_t stream) {
+                const CUtensorMap& md, const CUtensorMap& mp, const GemmParams& p, int pairs, cudaStream_t stream) {
   static bool configured[64] = {};
   if (int st = set_smem_once(mxb200_mx_gemm_pair_kernel<TN>, PairConfig<TN>::kSmemBytes, configured); st != MXB200_OK)
     return st;
   mxb200_mx_gemm_pair_kernel<TN><<<2 * pairs, kPairThreads, PairConfig<TN>::kSmemBytes, stream>>>(ma, mb, msa, msb, md,
-                                                                                                 p);
+                                                                                                 mp, p);
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return launch_status();
 }
@@ -1169,9 +1191,15 @@ int gemm(const void* a, const void* a_scale, const void* b, const void* b_scale,
     if (int st = make_scale_map(&msb, b_scale, N, K, 2); st != MXB200_OK)
       return st;
     const int pairs = static_cast<int>(std::min<int64_t>(tiles * p.splits, std::max(cap / 2, 1)));
+    CUtensorMap mp = md;  // unused without a K split
+    if (p.splits > 1) {
+      // partial half tiles, stacked: (tiles x splits x 2 halves x 128 rows, TN) fp32
+      if (int st = make_output_map(&mp, p.partials, tiles * p.splits * 256, plan.tile_n, true); st != MXB200_OK)
+        return st;
+    }
     if (plan.tile_n == 256)
-      return launch_pair<256>(ma, mb, msa, msb, md, p, pairs, s);
-    return launch_pair<192>(ma, mb, msa, msb, md, p, pairs, s);
+      return launch_pair<256>(ma, mb, msa, msb, md, mp, p, pairs, s);
+    return launch_pair<192>(ma, mb, msa, msb, md, mp, p, pairs, s);
   }
   if (int st = make_operand_map(&ma, a, M, K, kBM); st != MXB200_OK)
     return st;
@@ -1203,22 +1231,16 @@ extern "C" int mxb200_gemm_splits(int64_t M, int64_t N, int64_t K) {
   const mxb200::TilePlan plan = mxb200::plan_tiles(M, N, K, dev.sms);
   const int64_t tiles = plan.tiles(), slots = plan.slots;
   const int64_t k_tiles = K / 128;
-  // Splitting costs a round trip of fp32 partial tiles through the workspace, so it only pays when the tiles
-  // alone cannot fill the machine for two waves and every slice keeps a deep main loop.
-  if (tiles >= 2 * slots)
+  // Splitting K costs a round trip of fp32 partial tiles through the workspace plus a serial reduction, and on
+  // the d12-d26 shapes a narrower tile that fills a wave beat every split measured. It is kept for shapes that
+  // cannot fill even half the machine with tiles alone and have a deep K to share out.
+  if (tiles * 2 > slots)
     return 1;
   int best = 1;
-  double best_score = 0.0;
-  for (int s = 1; s <= 4; ++s) {
-    if (s > 1 && k_tiles / s < 32)
+  for (int s = 2; s <= 4; s *= 2) {
+    if (k_tiles / s < 32 || tiles * s > slots)
       break;
-    const int64_t units = tiles * s;
-    const int64_t waves = (units + slots - 1) / slots;
-    const double score = static_cast<double>(units) / static_cast<double>(waves * slots) * (s == 1 ? 1.0 : 0.9);
-    if (score > best_score + 1e-9) {
-      best_score = score;
-      best = s;
-    }
+    best = s;
   }
   return best;
 }

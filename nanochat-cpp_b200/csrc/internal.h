@@ -4,6 +4,7 @@
 #include <atomic>
 #include <cstdint>
 
+#include <cuda.h>
 #include <cuda_runtime.h>
 
 #include "mxb200.h"
@@ -21,6 +22,12 @@ struct DeviceInfo {
 
 // Properties of the current device, cached per device. Returns MXB200_ERR_DEVICE unless it is sm_100.
 int current_device(DeviceInfo* info);
+
+// cuTensorMapEncodeTiled, looked up through the runtime (no link-time dependency on libcuda); null if unavailable.
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_fn();
 
 inline bool aligned16(const void* p) {
   return (reinterpret_cast<uintptr_t>(p) & 15u) == 0;
