@@ -168,7 +168,15 @@ def run_gpu_arm(args):
             ev.record()
             gemm_events.append(ev)
 
-    step = DpStep(cfg, device, rank, world, gemm_hook=hook)
+    quant_events = []
+
+    def qhook(begin: bool):
+        if collect[0]:
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()
+            quant_events.append(ev)
+
+    step = DpStep(cfg, device, rank, world, gemm_hook=hook, quant_hook=qhook)
     flops = cfg.flops_per_step()
 
     def barrier():
@@ -198,6 +206,8 @@ def run_gpu_arm(args):
     ms_total = t_begin.elapsed_time(t_end)
     gemm_ms = sum(gemm_events[i].elapsed_time(gemm_events[i + 1]) for i in range(0, len(gemm_events), 2))
     n_gemm = len(gemm_events) // 2
+    quant_ms = sum(quant_events[i].elapsed_time(quant_events[i + 1]) for i in range(0, len(quant_events), 2))
+    n_quant = len(quant_events) // 2
     watchdog = nc.capi.device_status()
 
     # ---- end to end: the step's micro-batch activations come from pinned host memory, a result slice goes back
@@ -223,10 +233,10 @@ def run_gpu_arm(args):
     barrier()
     e2e_ms = e_begin.elapsed_time(e_end)
 
-    times = torch.tensor([ms_total, e2e_ms, gemm_ms], device=device, dtype=torch.float64)
+    times = torch.tensor([ms_total, e2e_ms, gemm_ms, quant_ms], device=device, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    ms_total, e2e_ms, gemm_ms = times.tolist()
+    ms_total, e2e_ms, gemm_ms, quant_ms = times.tolist()
 
     if rank == 0:
         peaks = measured_peaks()
@@ -256,6 +266,11 @@ def run_gpu_arm(args):
                          "unit": "TFLOP/s", "frac": achieved / fp8_peak, "traffic": None,
                          "peak_source": f"2 x bf16_tflops_sustained of {peaks['source']} (no FP8 GEMM peak was measured; the FP8 pipe runs at twice the bf16 rate)",
                          "launches": n_gemm, "avg_launch_us": gemm_ms * 1e3 / max(n_gemm, 1)},
+            "quantizer": {"bound": "hbm", "kernel": "mxb200_quantize_kernel", "achieved": cfg.quantized_bytes_per_step() * args.steps / (quant_ms * 1e-3) / 1e9,
+                          "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": cfg.quantized_bytes_per_step() * args.steps / (quant_ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                          "launches": n_quant, "ms_per_step": quant_ms / args.steps, "gb_per_step": cfg.quantized_bytes_per_step() / 1e9},
+            "ms_per_step_split": {"gemm": gemm_ms / args.steps, "quantize": quant_ms / args.steps,
+                                  "other": ms_per_step - (gemm_ms + quant_ms) / args.steps},
             "watchdog": watchdog,
         }
         if cpu is not None:

@@ -88,6 +88,21 @@ MXB200_API int mxb200_gemm_bf16(const void* a, const void* a_scale, const void* 
 MXB200_API int mxb200_gemm_f32(const void* a, const void* a_scale, const void* b, const void* b_scale, float* d, int64_t M,
                     int64_t N, int64_t K, const float* alpha, int accumulate, void* stream);
 
+/* Replaces nanochat::kernels::cutlass_mx_gemm_relu_square (src/nanochat/model/fp8/mx_gemm_kernel.h:24-27; used by the
+ * MLP forward, fp8.cpp:279-284): h (M, N) bf16 = a . b^T as mxb200_gemm_bf16, and in the same epilogue the outputs
+ * of mxb200_quantize_mx(h, RELU_SQUARE), bit for bit: q (M, N) e4m3 + q_scale, q_t (N, M) e4m3 + q_t_scale, each
+ * a whole contiguous tensor with its own swizzled scale buffer (M * N / 32 bytes). */
+MXB200_API int mxb200_gemm_relu_square(const void* a, const void* a_scale, const void* b, const void* b_scale, void* h,
+                                       void* q, void* q_scale, void* q_t, void* q_t_scale, int64_t M, int64_t N,
+                                       int64_t K, void* stream);
+
+/* Replaces nanochat::kernels::cutlass_mx_gemm_relu_square_bwd (mx_gemm_kernel.h:29-32; the MLP backward,
+ * fp8.cpp:318-323): ga = bf16(a . b^T) is not written; with h (M, N) bf16 read in the epilogue, the outputs of
+ * mxb200_quantize_mx_relu_square_bwd(ga, h), bit for bit: dh (M, N) e4m3 + dh_scale, dh_t (N, M) + dh_t_scale. */
+MXB200_API int mxb200_gemm_relu_square_bwd(const void* a, const void* a_scale, const void* b, const void* b_scale,
+                                           const void* h, void* dh, void* dh_scale, void* dh_t, void* dh_t_scale,
+                                           int64_t M, int64_t N, int64_t K, void* stream);
+
 /* Output kinds of the split-K entry point. */
 typedef enum mxb200_out_kind { MXB200_OUT_BF16 = 0, MXB200_OUT_F32 = 1 } mxb200_out_kind;
 

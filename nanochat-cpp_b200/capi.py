@@ -21,6 +21,7 @@ STATIC_SCRATCH_BYTES = 32 << 20
 # every symbol include/mxb200.h declares
 SYMBOLS = (
     "mxb200_quantize_mx", "mxb200_quantize_mx_relu_square_bwd", "mxb200_gemm_bf16", "mxb200_gemm_f32",
+    "mxb200_gemm_relu_square", "mxb200_gemm_relu_square_bwd",
     "mxb200_gemm_splits", "mxb200_gemm_workspace_bytes", "mxb200_gemm_splitk", "mxb200_gemm_splitk_static",
     "mxb200_strerror",
     "mxb200_device_status", "mxb200_set_gemm_config", "mxb200_launch_count", "mxb200_version",
@@ -49,6 +50,8 @@ def _load() -> ctypes.CDLL:
     lib.mxb200_quantize_mx_relu_square_bwd.argtypes = [vp, vp, i64, i64, MxOut, MxOut, i32, vp]
     lib.mxb200_gemm_bf16.argtypes = [vp, vp, vp, vp, vp, vp, i64, i64, i64, vp]
     lib.mxb200_gemm_f32.argtypes = [vp, vp, vp, vp, vp, i64, i64, i64, vp, i32, vp]
+    lib.mxb200_gemm_relu_square.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, i64, i64, i64, vp]
+    lib.mxb200_gemm_relu_square_bwd.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, i64, i64, i64, vp]
     lib.mxb200_gemm_splits.argtypes = [i64, i64, i64]
     lib.mxb200_gemm_workspace_bytes.argtypes = [i64, i64, i64, i32]
     lib.mxb200_gemm_workspace_bytes.restype = ctypes.c_size_t

@@ -60,6 +60,13 @@ constexpr uint32_t kTmemCols = 512;
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
 
 enum OutKind : int { kOutBf16 = 0, kOutF32 = 1 };
+// What the epilogue does besides (or instead of) writing the bf16 output.
+enum Fuse : int {
+  kFuseNone = 0,
+  kFuseReluSquare = 1,     // h = bf16(acc) written; MX(bf16(relu(h)^2)) in both layouts written
+  kFuseReluSquareBwd = 2,  // ga = bf16(acc) not written; MX(bf16(h > 0 ? ga * 2h : 0)) in both layouts written
+};
+
 
 // where a wait gave up (stored in the watchdog word's low byte)
 enum WaitSite : uint32_t {
@@ -105,6 +112,13 @@ struct GemmParams {
   int out_kind;
   int accumulate;
   bool wide;  // d and resid are 32-byte aligned: 256-bit global accesses
+  // fused MX quantization of the output (CTA-pair kernel): scales of q (rows of the output) and of q_t (its
+  // columns), each at its buffer's first tile, with the tiles-per-128-rows of each buffer; h_in: relu^2 backward
+  uint8_t* q_scale;
+  uint8_t* qt_scale;
+  int q_scale_tiles, qt_scale_tiles;
+  const void* h_in;
+  bool floor_rule;
 };
 
 struct Barriers {
@@ -608,6 +622,170 @@ __global__ void __launch_bounds__(kThreads, 1)
 }
 
 
+// ------------------------------------------------------------------------------------------------ fused quantizer
+//
+// The MX quantizer run on a 32 x 32 block of the accumulator while it is still in registers, for the two GEMMs of
+// the relu^2 MLP whose output only exists to be quantized (nanochat-cpp fuses the same two:
+// cutlass_mx_gemm_relu_square / cutlass_mx_gemm_relu_square_bwd, src/nanochat/model/fp8/mx_gemm_kernel.cu:353-389,
+// used at fp8.cpp:279-284, 318-323). Same bytes as the GEMM followed by mxb200_quantize_mx.
+//   rows:    a thread holds its row's 32 columns = one scale block: no communication.
+//   columns: the block goes through shared memory (bf16, the 64-byte-swizzled 2 KB tile the output store uses),
+//            lane j then reads column j's 32 rows = one scale block of the transposed layout.
+// Both results are parked as 32 rows x 32 bytes and leave by TMA store; scale bytes go straight to their swizzled
+// positions. Layout of `stage` (6 KB per warp): [0,2K) output rows, [2K,4K) transpose tile, [4K,5K) q, [5K,6K) q_t.
+
+__device__ __forceinline__ uint32_t e4m3x4(float a, float b, float c, float d) {
+  uint16_t lo, hi;
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %2, %1;" : "=h"(lo) : "f"(a), "f"(b));
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %2, %1;" : "=h"(hi) : "f"(c), "f"(d));
+  return static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16);
+}
+
+__device__ __forceinline__ float bf16_round(float v) {
+  return __bfloat162float(__float2bfloat16(v));
+}
+
+// The relu^2 backward form's second input: this lane's four 16-byte pieces of the 32 x 32 bf16 block of h at
+// (warp_row0, col). Zeros outside the matrix.
+__device__ __forceinline__ void load_h_pieces(const GemmParams& p, int lane, int warp_row0, int col, uint4* pieces) {
+  const bool inside = warp_row0 < p.M && col < p.N;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int r = j * 8 + (lane >> 2), piece = lane & 3;
+    pieces[j] = inside ? __ldg(reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(p.h_in) +
+                                                              (static_cast<int64_t>(warp_row0) + r) * p.N + col + piece * 8))
+                       : make_uint4(0, 0, 0, 0);
+  }
+}
+
+template <int kFuse>
+__device__ __forceinline__ void fused_quantize_chunk(const GemmParams& p, const CUtensorMap* map_d,
+                                                     const CUtensorMap* map_q, const CUtensorMap* map_qt,
+                                                     unsigned char* stage, int lane, const float* acc, int64_t row,
+                                                     int col, int warp_row0, bool valid, const uint4* h_pieces) {
+  unsigned char* st_out = stage;
+  unsigned char* st_tr = stage + 2048;
+  unsigned char* st_q = stage + 4096;
+  unsigned char* st_qt = stage + 5120;
+  if (lane == 0)
+    tma_store_wait_read<0>();  // the previous chunk's stores have been read out of all four buffers
+  __syncwarp();
+
+  // ---- the values to quantize, v[32], bf16-exact
+  float v[32];
+  if constexpr (kFuse == kFuseReluSquare) {
+    uint32_t o[16];
+#pragma unroll
+    for (int k = 0; k < 16; ++k) {
+      o[k] = pack_bf16x2(acc[2 * k], acc[2 * k + 1]);
+      const float h0 = __uint_as_float(o[k] << 16), h1 = __uint_as_float(o[k] & 0xffff0000u);
+      const float r0 = h0 <= 0.f ? 0.f : h0, r1 = h1 <= 0.f ? 0.f : h1;
+      v[2 * k] = bf16_round(r0 * r0);
+      v[2 * k + 1] = bf16_round(r1 * r1);
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j)  // h itself leaves as the plain epilogue's output does
+      *reinterpret_cast<uint4*>(st_out + lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4)) =
+            make_uint4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
+  } else {
+    // h's 32 x 32 block was loaded coalesced (load_h_pieces: 4 lanes per 64-byte row segment, 8 rows per
+    // instruction, issued a chunk ahead) and is handed to the row owners through the otherwise unused output buffer
+    uint32_t hw[16];
+    if (warp_row0 < p.M && col < p.N) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int r = j * 8 + (lane >> 2), piece = lane & 3;
+        *reinterpret_cast<uint4*>(st_out + r * 64 + ((piece ^ ((r >> 1) & 3)) << 4)) = h_pieces[j];
+      }
+      __syncwarp();
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const uint4 t = *reinterpret_cast<const uint4*>(st_out + lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4));
+        hw[4 * j] = t.x, hw[4 * j + 1] = t.y, hw[4 * j + 2] = t.z, hw[4 * j + 3] = t.w;
+      }
+    } else {
+#pragma unroll
+      for (int k = 0; k < 16; ++k)
+        hw[k] = 0;
+    }
+#pragma unroll
+    for (int k = 0; k < 16; ++k) {
+      const float g0 = bf16_round(acc[2 * k]), g1 = bf16_round(acc[2 * k + 1]);
+      const float h0 = __uint_as_float(hw[k] << 16), h1 = __uint_as_float(hw[k] & 0xffff0000u);
+      v[2 * k] = bf16_round(h0 <= 0.f ? 0.f : g0 * (2.f * h0));
+      v[2 * k + 1] = bf16_round(h1 <= 0.f ? 0.f : g1 * (2.f * h1));
+    }
+  }
+
+  // ---- rows: this thread's 32 values are one block
+  {
+    float m = 0.f;
+#pragma unroll
+    for (int k = 0; k < 32; ++k)
+      m = fmaxf(m, fabsf(v[k]));
+    const int e = mx_exponent(__float_as_uint(m), p.floor_rule);
+    const float mul = __uint_as_float(mx_multiplier_bits(e));
+    uint32_t w[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k)
+      w[k] = e4m3x4(v[4 * k] * mul, v[4 * k + 1] * mul, v[4 * k + 2] * mul, v[4 * k + 3] * mul);
+    *reinterpret_cast<uint4*>(st_q + lane * 32) = make_uint4(w[0], w[1], w[2], w[3]);
+    *reinterpret_cast<uint4*>(st_q + lane * 32 + 16) = make_uint4(w[4], w[5], w[6], w[7]);
+    if (valid) {
+      const int b = col >> 5;
+      p.q_scale[(static_cast<int64_t>(row >> 7) * p.q_scale_tiles + (b >> 2)) * kScaleTileBytes +
+                mx_scale_tile_offset(static_cast<int>(row & 127), b)] = static_cast<uint8_t>(e);
+    }
+  }
+
+  // ---- columns: through the transpose tile, written column-major (each store instruction puts one column's 32
+  // rows in 64 contiguous bytes, conflict-free), so that a lane reads its column as four 16-byte vectors
+#pragma unroll
+  for (int k = 0; k < 32; ++k)  // bf16-exact values: the top 16 bits are the bf16
+    *reinterpret_cast<uint16_t*>(st_tr + k * 64 + lane * 2) = static_cast<uint16_t>(__float_as_uint(v[k]) >> 16);
+  __syncwarp();
+  {
+    float c[32];
+    float m = 0.f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const uint4 t = *reinterpret_cast<const uint4*>(st_tr + lane * 64 + j * 16);
+      const uint32_t w[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        c[8 * j + 2 * k] = __uint_as_float(w[k] << 16);
+        c[8 * j + 2 * k + 1] = __uint_as_float(w[k] & 0xffff0000u);
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < 32; ++r)
+      m = fmaxf(m, fabsf(c[r]));
+    const int e = mx_exponent(__float_as_uint(m), p.floor_rule);
+    const float mul = __uint_as_float(mx_multiplier_bits(e));
+    uint32_t w[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k)
+      w[k] = e4m3x4(c[4 * k] * mul, c[4 * k + 1] * mul, c[4 * k + 2] * mul, c[4 * k + 3] * mul);
+    *reinterpret_cast<uint4*>(st_qt + lane * 32) = make_uint4(w[0], w[1], w[2], w[3]);
+    *reinterpret_cast<uint4*>(st_qt + lane * 32 + 16) = make_uint4(w[4], w[5], w[6], w[7]);
+    const int n = col + lane;  // row of the transposed layout
+    if (warp_row0 < p.M && n < p.N) {
+      const int b = warp_row0 >> 5;
+      p.qt_scale[(static_cast<int64_t>(n >> 7) * p.qt_scale_tiles + (b >> 2)) * kScaleTileBytes +
+                 mx_scale_tile_offset(n & 127, b)] = static_cast<uint8_t>(e);
+    }
+  }
+  fence_proxy_async_smem();
+  __syncwarp();
+  if (lane == 0 && warp_row0 < p.M && col < p.N) {
+    if constexpr (kFuse == kFuseReluSquare)
+      tma_store_2d(map_d, st_out, col, warp_row0);
+    tma_store_2d(map_q, st_q, col, warp_row0);
+    tma_store_2d(map_qt, st_qt, warp_row0, col);
+    tma_store_commit();
+  }
+}
+
 // ------------------------------------------------------------------------------------------------ CTA-pair kernel
 //
 // Two CTAs on the SMs of one TPC (a cluster of 2) share one 256 x 256 output tile: tcgen05.mma.cta_group::2 reads
@@ -628,12 +806,15 @@ __global__ void __launch_bounds__(kThreads, 1)
 // address at an odd column (a tile starting 32 or 96 rows into a scale tile, as a 224-wide tiling would) is a
 // misaligned-address fault, so tile widths are multiples of 64.
 constexpr int kEpiStageBytes = 2048;       // one epilogue warp's staging buffer for TMA stores
+constexpr int kEpiFusedBytes = 6144;       // ... with a fused quantizer: output rows, transpose tile, q rows, q_t rows
+
 constexpr int kPairThreads = 320;          // producer warp, MMA warp, 8 epilogue warps
 constexpr int kPairEpilogueThreads = 256;  // two warps per TMEM lane quarter, each half of the tile's columns
 
-template <int TN>
+template <int TN, int kFuse = kFuseNone>
 struct PairConfig {
   static_assert(TN == 192 || TN == 256, "tile width");
+  static constexpr int kEpiBytes = kFuse == kFuseNone ? kEpiStageBytes : kEpiFusedBytes;
   static constexpr int kTileM = 256, kTileN = TN;
   static constexpr int kBRows = TN / 2;                // this CTA's rows of B
   static constexpr int kSfbTiles = 2;
@@ -641,28 +822,30 @@ struct PairConfig {
   static constexpr uint32_t kBBytes = kBRows * kBK;
   static constexpr uint32_t kSfBytes = kScaleTileBytes * (1 + kSfbTiles);  // A: own 128 rows; B: all its tiles
   static constexpr uint32_t kTxPerCta = kABytes + kBBytes + kSfBytes;
-  static constexpr int kStages = TN == 192 ? 7 : 6;
+  static constexpr int kStages = (TN == 192 ? 7 : 6) - (kFuse == kFuseNone ? 0 : 1);
   static constexpr bool kOverlap = TN == 256;
   static constexpr uint32_t kAcc0 = 0, kAcc1 = kOverlap ? 224 : TN;
   static constexpr uint32_t kSfaCol = kOverlap ? 480 : 2 * TN, kSfbCol = kSfaCol + 4;
   static constexpr size_t kSmemBytes = 1024 + static_cast<size_t>(kStages) * (kABytes + kBBytes + kSfBytes) +
-                                       kPairEpilogueThreads / 32 * kEpiStageBytes + 256;
+                                       kPairEpilogueThreads / 32 * kEpiBytes + 256;
 };
 
-template <int TN>
+template <int TN, int kFuse>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
       mxb200_mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                                  const __grid_constant__ CUtensorMap map_sfa,
                                  const __grid_constant__ CUtensorMap map_sfb,
                                  const __grid_constant__ CUtensorMap map_d,
-                                 const __grid_constant__ CUtensorMap map_part, const GemmParams p) {
-  using C = PairConfig<TN>;
+                                 const __grid_constant__ CUtensorMap map_part,
+                                 const __grid_constant__ CUtensorMap map_q,
+                                 const __grid_constant__ CUtensorMap map_qt, const GemmParams p) {
+  using C = PairConfig<TN, kFuse>;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   unsigned char* s_a = smem;
   unsigned char* s_b = s_a + C::kStages * C::kABytes;
   unsigned char* s_epi = s_b + C::kStages * C::kBBytes;  // 2 KB per epilogue warp: 32 rows x 64 bytes
-  unsigned char* s_sf = s_epi + kPairEpilogueThreads / 32 * kEpiStageBytes;  // per stage: A's tile, B's two tiles
+  unsigned char* s_sf = s_epi + kPairEpilogueThreads / 32 * C::kEpiBytes;  // per stage: A's tile, B's two tiles
   Barriers* bars = reinterpret_cast<Barriers*>(s_sf + C::kStages * C::kSfBytes);
 
   const int warp = static_cast<int>(threadIdx.x) >> 5, lane = static_cast<int>(threadIdx.x) & 31;
@@ -694,6 +877,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
     prefetch_tensormap(&map_d);
     if (p.splits > 1)
       prefetch_tensormap(&map_part);
+    if (kFuse != kFuseNone) {
+      prefetch_tensormap(&map_q);
+      prefetch_tensormap(&map_qt);
+    }
   }
   if (warp == 1) {
     tmem_alloc_pair(&bars->tmem_base, kTmemCols);
@@ -828,10 +1015,17 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
     const uint32_t empty_leader[2] = {map_to_cta(smem_u32(&bars->tmem_empty[0]), 0),
                                       map_to_cta(smem_u32(&bars->tmem_empty[1]), 0)};
     const uint32_t overlap_leader = map_to_cta(smem_u32(&bars->overlap_free), 0);
-    unsigned char* stage = s_epi + (warp - 2) * kEpiStageBytes;
+    unsigned char* stage = s_epi + (warp - 2) * C::kEpiBytes;
     for (int unit = pair; ok && unit < total_units; unit += num_pairs, ++local) {
       const TileCoord tc = decode_unit(p, unit);
       const uint32_t buf = local & 1u, use = local >> 1;
+      // the relu^2 backward form reads h: the first chunk's block is requested before the accumulator is waited for
+      uint4 h_pieces[2][4];
+      if constexpr (kFuse == kFuseReluSquareBwd) {
+        const int c0 = (C::kOverlap && buf == 0 && col_half == 1) ? kChunks - 1 : col_half * kMine;
+        load_h_pieces(p, lane, tc.m * C::kTileM + static_cast<int>(rank) * 128 + quarter * 32, tc.n * C::kTileN + c0 * 32,
+                      h_pieces[0]);
+      }
       if (!wait_bounded(&bars->tmem_full[buf], use & 1u, bars, kSiteEpilogueFull)) {
         ok = false;
         break;
@@ -862,8 +1056,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
           break;
         const int c = chunk_of(i);
         tmem_ld_wait();
-        if (i + 1 < n_mine)
+        if (i + 1 < n_mine) {
           tmem_ld_32x32b_x32(acc_t + chunk_of(i + 1) * 32, r[(i + 1) & 1]);
+          if constexpr (kFuse == kFuseReluSquareBwd)
+            load_h_pieces(p, lane, warp_row0, col0 + chunk_of(i + 1) * 32, h_pieces[(i + 1) & 1]);
+        }
         if (i == 0 && owns_shared) {
           tcgen05_fence_before_sync();
           __syncwarp();
@@ -876,6 +1073,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
           const int part_row0 = static_cast<int>(half_index) * 128 + quarter * 32;
           store_rows_tma(&map_part, stage, lane, r[i & 1], c * 32, part_row0, true);
           store_rows_tma(&map_part, stage, lane, r[i & 1] + 16, c * 32 + 16, part_row0, true);
+        } else if constexpr (kFuse != kFuseNone) {
+          fused_quantize_chunk<kFuse>(p, &map_d, &map_q, &map_qt, stage, lane, reinterpret_cast<const float*>(r[i & 1]),
+                                      row, col, warp_row0, row_ok && col < p.N, h_pieces[i & 1]);
         } else {
           const bool valid = row_ok && col < p.N;
           const bool issue = warp_row0 < p.M && col < p.N;
@@ -1041,10 +1241,12 @@ struct TilePlan {
   int64_t counters() const { return tiles() * (pair ? 2 : 1); }
 };
 
-TilePlan plan_tiles(int64_t M, int64_t N, int64_t K, int sms) {
-  const int forced = g_tile_n.load();
+TilePlan plan_tiles(int64_t M, int64_t N, int64_t K, int sms, bool need_pair = false) {
+  int forced = g_tile_n.load();
+  if (need_pair && (forced == 128 || forced == 256))
+    forced = 0;  // the fused-quantize epilogues exist in the CTA-pair kernel only
   TilePlan t{};
-  if (forced == 512 || forced == 384 || (forced == 0 && M >= 256 && N >= 256)) {
+  if (forced == 512 || forced == 384 || need_pair || (forced == 0 && M >= 256 && N >= 256)) {
     t.pair = true, t.tile_m = 256, t.slots = std::max(sms / 2, 1);
     if (forced == 512) {
       t.tile_n = 256;
@@ -1110,30 +1312,76 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, in
   return launch_status();
 }
 
-template <int TN>
-int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& msa, const CUtensorMap& msb,
-                const CUtensorMap& md, const CUtensorMap& mp, const GemmParams& p, int pairs, cudaStream_t stream) {
+struct PairMaps {
+  CUtensorMap a, b, sfa, sfb, d, part, q, qt;
+};
+
+template <int TN, int kFuse>
+int launch_pair(const PairMaps& m, const GemmParams& p, int pairs, cudaStream_t stream) {
+  using C = PairConfig<TN, kFuse>;
   static bool configured[64] = {};
-  if (int st = set_smem_once(mxb200_mx_gemm_pair_kernel<TN>, PairConfig<TN>::kSmemBytes, configured); st != MXB200_OK)
+  if (int st = set_smem_once(mxb200_mx_gemm_pair_kernel<TN, kFuse>, C::kSmemBytes, configured); st != MXB200_OK)
     return st;
-  mxb200_mx_gemm_pair_kernel<TN><<<2 * pairs, kPairThreads, PairConfig<TN>::kSmemBytes, stream>>>(ma, mb, msa, msb, md,
-                                                                                                 mp, p);
+  mxb200_mx_gemm_pair_kernel<TN, kFuse><<<2 * pairs, kPairThreads, C::kSmemBytes, stream>>>(m.a, m.b, m.sfa, m.sfb, m.d,
+                                                                                           m.part, m.q, m.qt, p);
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return launch_status();
 }
 
+template <int kFuse>
+int launch_pair_width(int tile_n, const PairMaps& m, const GemmParams& p, int pairs, cudaStream_t stream) {
+  return tile_n == 256 ? launch_pair<256, kFuse>(m, p, pairs, stream) : launch_pair<192, kFuse>(m, p, pairs, stream);
+}
+
+// (rows, cols) row-major bytes, box = 32 rows x 32 bytes: what one epilogue warp stores of a quantized layout
+int make_bytes_map(CUtensorMap* map, void* base, int64_t rows, int64_t cols) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr)
+    return MXB200_ERR_DRIVER;
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(cols)};
+  const cuuint32_t box[2] = {32, 32};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, base, dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? MXB200_OK : MXB200_ERR_DRIVER;
+}
+
+// Outputs of a fused-quantize GEMM (fuse != kFuseNone); see include/mxb200.h.
+struct FusedOut {
+  int fuse = kFuseNone;
+  void* q = nullptr;
+  void* q_scale = nullptr;
+  void* q_t = nullptr;
+  void* q_t_scale = nullptr;
+  const void* h_in = nullptr;
+};
+
 int gemm(const void* a, const void* a_scale, const void* b, const void* b_scale, void* d, int out_kind,
          const void* resid, int64_t M, int64_t N, int64_t K, const float* alpha, int accumulate, int splits,
-         void* workspace, size_t workspace_bytes, void* stream) {
+         void* workspace, size_t workspace_bytes, void* stream, const FusedOut& fused = FusedOut{}) {
   DeviceInfo dev;
   if (int s = current_device(&dev); s != MXB200_OK)
     return s;
-  if (a == nullptr || a_scale == nullptr || b == nullptr || b_scale == nullptr || d == nullptr)
+  const bool fusing = fused.fuse != kFuseNone;
+  if (a == nullptr || a_scale == nullptr || b == nullptr || b_scale == nullptr ||
+      (d == nullptr && fused.fuse != kFuseReluSquareBwd))
     return MXB200_ERR_NULL;
+  if (fusing) {
+    if (fused.q == nullptr || fused.q_scale == nullptr || fused.q_t == nullptr || fused.q_t_scale == nullptr ||
+        (fused.fuse == kFuseReluSquareBwd && fused.h_in == nullptr))
+      return MXB200_ERR_NULL;
+    if (!aligned16(fused.q) || !aligned16(fused.q_scale) || !aligned16(fused.q_t) || !aligned16(fused.q_t_scale) ||
+        (fused.h_in != nullptr && !aligned16(fused.h_in)))
+      return MXB200_ERR_ALIGNMENT;
+    if (out_kind != kOutBf16 || resid != nullptr || splits != 1)
+      return MXB200_ERR_ARGUMENT;
+  }
   if (M <= 0 || N <= 0 || K <= 0 || M % 128 != 0 || N % 128 != 0 || K % 128 != 0 || M > (1 << 30) || N > (1 << 30) ||
       K > (1 << 30))
     return MXB200_ERR_SHAPE;
-  if (!aligned16(a) || !aligned16(a_scale) || !aligned16(b) || !aligned16(b_scale) || !aligned16(d) ||
+  if (!aligned16(a) || !aligned16(a_scale) || !aligned16(b) || !aligned16(b_scale) || (d != nullptr && !aligned16(d)) ||
       (resid != nullptr && !aligned16(resid)))
     return MXB200_ERR_ALIGNMENT;
   if (out_kind != kOutBf16 && out_kind != kOutF32)
@@ -1144,7 +1392,7 @@ int gemm(const void* a, const void* a_scale, const void* b, const void* b_scale,
   if (splits < 1 || splits > k_tiles || splits > 64)
     return MXB200_ERR_ARGUMENT;
 
-  const TilePlan plan = plan_tiles(M, N, K, dev.sms);
+  const TilePlan plan = plan_tiles(M, N, K, dev.sms, fusing);
   GemmParams p{};
   p.a_scale = static_cast<const uint8_t*>(a_scale);
   p.b_scale = static_cast<const uint8_t*>(b_scale);
@@ -1160,7 +1408,14 @@ int gemm(const void* a, const void* a_scale, const void* b, const void* b_scale,
   p.panel = std::min(p.tiles_n, 8);
   p.out_kind = out_kind;
   p.accumulate = out_kind == kOutF32 ? (accumulate != 0) : 0;
-  p.wide = (reinterpret_cast<uintptr_t>(d) & 31u) == 0 && (reinterpret_cast<uintptr_t>(resid) & 31u) == 0;
+  p.wide = (reinterpret_cast<uintptr_t>(d) & 31u) == 0 && (reinterpret_cast<uintptr_t>(resid) & 31u) == 0 &&
+           (reinterpret_cast<uintptr_t>(fused.h_in) & 31u) == 0;
+  p.q_scale = static_cast<uint8_t*>(fused.q_scale);
+  p.qt_scale = static_cast<uint8_t*>(fused.q_t_scale);
+  p.q_scale_tiles = static_cast<int>(N / 128);
+  p.qt_scale_tiles = static_cast<int>(M / 128);
+  p.h_in = fused.h_in;
+  p.floor_rule = false;
   const int64_t tiles = plan.tiles();
   if (tiles * p.splits > 0x7fffffffLL)
     return MXB200_ERR_SHAPE;
@@ -1179,27 +1434,40 @@ int gemm(const void* a, const void* a_scale, const void* b, const void* b_scale,
   const int cap = g_max_ctas.load() > 0 ? g_max_ctas.load() : dev.sms;
   CUtensorMap ma, mb;
   if (plan.pair) {
-    CUtensorMap msa, msb, md;
-    if (int st = make_output_map(&md, d, M, N, out_kind == kOutF32); st != MXB200_OK)
+    PairMaps m;
+    if (int st = make_operand_map(&m.a, a, M, K, 128); st != MXB200_OK)
       return st;
-    if (int st = make_operand_map(&ma, a, M, K, 128); st != MXB200_OK)
+    if (int st = make_operand_map(&m.b, b, N, K, plan.tile_n / 2); st != MXB200_OK)
       return st;
-    if (int st = make_operand_map(&mb, b, N, K, plan.tile_n / 2); st != MXB200_OK)
+    if (int st = make_scale_map(&m.sfa, a_scale, M, K, 1); st != MXB200_OK)
       return st;
-    if (int st = make_scale_map(&msa, a_scale, M, K, 1); st != MXB200_OK)
+    if (int st = make_scale_map(&m.sfb, b_scale, N, K, 2); st != MXB200_OK)
       return st;
-    if (int st = make_scale_map(&msb, b_scale, N, K, 2); st != MXB200_OK)
-      return st;
-    const int pairs = static_cast<int>(std::min<int64_t>(tiles * p.splits, std::max(cap / 2, 1)));
-    CUtensorMap mp = md;  // unused without a K split
+    if (d != nullptr) {
+      if (int st = make_output_map(&m.d, d, M, N, out_kind == kOutF32); st != MXB200_OK)
+        return st;
+    } else {
+      m.d = m.a;  // never used: the relu^2 backward form writes no plain output
+    }
+    m.part = m.d;  // unused without a K split
     if (p.splits > 1) {
       // partial half tiles, stacked: (tiles x splits x 2 halves x 128 rows, TN) fp32
-      if (int st = make_output_map(&mp, p.partials, tiles * p.splits * 256, plan.tile_n, true); st != MXB200_OK)
+      if (int st = make_output_map(&m.part, p.partials, tiles * p.splits * 256, plan.tile_n, true); st != MXB200_OK)
         return st;
     }
-    if (plan.tile_n == 256)
-      return launch_pair<256>(ma, mb, msa, msb, md, mp, p, pairs, s);
-    return launch_pair<192>(ma, mb, msa, msb, md, mp, p, pairs, s);
+    m.q = m.qt = m.d;
+    if (fusing) {
+      if (int st = make_bytes_map(&m.q, fused.q, M, N); st != MXB200_OK)
+        return st;
+      if (int st = make_bytes_map(&m.qt, fused.q_t, N, M); st != MXB200_OK)
+        return st;
+    }
+    const int pairs = static_cast<int>(std::min<int64_t>(tiles * p.splits, std::max(cap / 2, 1)));
+    if (fused.fuse == kFuseReluSquare)
+      return launch_pair_width<kFuseReluSquare>(plan.tile_n, m, p, pairs, s);
+    if (fused.fuse == kFuseReluSquareBwd)
+      return launch_pair_width<kFuseReluSquareBwd>(plan.tile_n, m, p, pairs, s);
+    return launch_pair_width<kFuseNone>(plan.tile_n, m, p, pairs, s);
   }
   if (int st = make_operand_map(&ma, a, M, K, kBM); st != MXB200_OK)
     return st;
@@ -1319,3 +1587,20 @@ extern "C" __attribute__((visibility("default"))) int mxb200_trace_read(unsigned
   return cudaMemcpyFromSymbol(out, mxb200::g_trace, sizeof(unsigned long long) * n) == cudaSuccess ? 0 : 1;
 }
 #endif
+
+extern "C" int mxb200_gemm_relu_square(const void* a, const void* a_scale, const void* b, const void* b_scale, void* h,
+                                       void* q, void* q_scale, void* q_t, void* q_t_scale, int64_t M, int64_t N,
+                                       int64_t K, void* stream) {
+  mxb200::FusedOut f;
+  f.fuse = mxb200::kFuseReluSquare, f.q = q, f.q_scale = q_scale, f.q_t = q_t, f.q_t_scale = q_t_scale;
+  return mxb200::gemm(a, a_scale, b, b_scale, h, mxb200::kOutBf16, nullptr, M, N, K, nullptr, 0, 1, nullptr, 0, stream, f);
+}
+
+extern "C" int mxb200_gemm_relu_square_bwd(const void* a, const void* a_scale, const void* b, const void* b_scale,
+                                           const void* h, void* dh, void* dh_scale, void* dh_t, void* dh_t_scale,
+                                           int64_t M, int64_t N, int64_t K, void* stream) {
+  mxb200::FusedOut f;
+  f.fuse = mxb200::kFuseReluSquareBwd, f.q = dh, f.q_scale = dh_scale, f.q_t = dh_t, f.q_t_scale = dh_t_scale, f.h_in = h;
+  return mxb200::gemm(a, a_scale, b, b_scale, nullptr, mxb200::kOutBf16, nullptr, M, N, K, nullptr, 0, 1, nullptr, 0,
+                      stream, f);
+}

@@ -31,6 +31,7 @@ class StepConfig:
     vocab: int = 32768
     tokens: int = 16384          # per rank: batch 8 x sequence 2048
     chunk_rows: int = 2048       # lm_head row chunk
+    fused_mlp: bool = True       # relu^2 / relu^2-backward quantization inside the fc / proj-dgrad GEMM epilogues
 
     @property
     def linear_shapes(self):
@@ -44,6 +45,20 @@ class StepConfig:
     @property
     def lm_head_params(self) -> int:
         return self.vocab * self.n_embd
+
+    def quantized_bytes_per_step(self) -> float:
+        """Algorithmic HBM bytes of every quantizer launch of a step: input read once (2 B bf16, 4 B fp32 weights,
+        two bf16 inputs for the relu^2 backward) plus (1 + 1/32) B per element and written layout."""
+        M, C, V = self.tokens, self.n_embd, self.vocab
+        both = 2 * (1 + 1 / 32)
+        act = (3 * M * C) * (2 + both)                                             # x_attn, y_att, x_mlp
+        grad = (2 * M * C + M * 3 * C) * (2 + both)                                # dy_proj, dy_o, dy_qkv
+        if not self.fused_mlp:                                                     # relu^2(h) and dh as own passes
+            act += (M * 4 * C) * (2 + both)
+            grad += (M * 4 * C) * (4 + both)
+        weights = self.layer_params * (4 + both)
+        lm = (M * C) * (2 + both) + (M * V) * (2 + both) + self.lm_head_params * (4 + both)
+        return self.n_layer * (act + grad + weights) + lm
 
     def flops_per_step(self) -> float:
         """2MNK over every GEMM: forward, dgrad and wgrad of each Linear."""
@@ -110,13 +125,16 @@ def _student_t(shape, nu: float, gen, device) -> torch.Tensor:
 
 
 class DpStep:
-    """Buffers and launch sequence of one rank's step. `gemm_hook(begin: bool)` (optional) is called right before
-    and right after every GEMM launch so a benchmark can bracket them with events."""
+    """Buffers and launch sequence of one rank's step. `gemm_hook(begin: bool)` and `quant_hook(begin: bool)`
+    (optional) are called right before and right after every GEMM / quantizer launch so a benchmark can bracket
+    them with events."""
 
     def __init__(self, cfg: StepConfig, device, rank: int = 0, world: int = 1, input_sets: int = 2,
-                 gemm_hook: Optional[Callable[[bool], None]] = None):
+                 gemm_hook: Optional[Callable[[bool], None]] = None,
+                 quant_hook: Optional[Callable[[bool], None]] = None):
         self.cfg, self.device, self.rank, self.world = cfg, device, rank, world
         self.hook = gemm_hook
+        self.qhook = quant_hook
         M, C, V = cfg.tokens, cfg.n_embd, cfg.vocab
         gen = torch.Generator(device=device).manual_seed(1000 + rank)
         bf = torch.bfloat16
@@ -179,7 +197,14 @@ class DpStep:
 
     def _quant(self, x, q: nc.Fp8Tensor, relu_square=False):
         out, out_t = nc.mx_outs(q)
+        self._quant_into(x, relu_square, out, out_t)
+
+    def _quant_into(self, x, relu_square, out, out_t):
+        if self.qhook:
+            self.qhook(True)
         nc.quantize_mx_into(x, relu_square, out, out_t)
+        if self.qhook:
+            self.qhook(False)
 
     def quantize_weights(self):
         """Once per optimizer step (the reference's weight cache, fp8.cpp:516-536): fp32 masters -> both layouts."""
@@ -195,21 +220,44 @@ class DpStep:
         self._quant(self.y_att[s], self.yq_att[l])
         self._gemm(self.out_c, self.yq_att[l].data, self.yq_att[l].inv_scale, wq[1].data, wq[1].inv_scale, self.resid[s])
         self._quant(self.x_mlp[s], self.xq_mlp[l])
-        self._gemm(self.h[l], self.xq_mlp[l].data, self.xq_mlp[l].inv_scale, wq[2].data, wq[2].inv_scale)
-        self._quant(self.h[l], self.aq[l], relu_square=True)
+        if self.cfg.fused_mlp:
+            # fc GEMM writes h and, from the same epilogue, MX(relu(h)^2) in both layouts (fp8.cpp:279-284)
+            if self.hook:
+                self.hook(True)
+            nc.mx_gemm_relu_square(self.h[l], self.aq[l].data, self.aq[l].inv_scale, self.aq[l].data_t,
+                                   self.aq[l].inv_scale_t, self.xq_mlp[l].data, self.xq_mlp[l].inv_scale, wq[2].data,
+                                   wq[2].inv_scale)
+            if self.hook:
+                self.hook(False)
+        else:
+            self._gemm(self.h[l], self.xq_mlp[l].data, self.xq_mlp[l].inv_scale, wq[2].data, wq[2].inv_scale)
+            self._quant(self.h[l], self.aq[l], relu_square=True)
         self._gemm(self.out_c, self.aq[l].data, self.aq[l].inv_scale, wq[3].data, wq[3].inv_scale, self.resid[s])
 
     def layer_backward(self, l: int, s: int):
         wq, b = self.wq[l], self.bucket
         # MLP proj: dA = dY . W, dW = dY^T . A
         self._quant(self.dy_proj[s], self.gq_c)
-        self._gemm(self.da, self.gq_c.data, self.gq_c.inv_scale, wq[3].data_t, wq[3].inv_scale_t)
+        if self.cfg.fused_mlp:
+            # dgrad GEMM whose epilogue reads h and emits MX(dh) directly; dA is never written (fp8.cpp:318-323)
+            if self.hook:
+                self.hook(True)
+            nc.mx_gemm_relu_square_bwd(self.gq_c.data, self.gq_c.inv_scale, wq[3].data_t, wq[3].inv_scale_t, self.h[l],
+                                       self.gq_4c.data, self.gq_4c.inv_scale, self.gq_4c.data_t, self.gq_4c.inv_scale_t)
+            if self.hook:
+                self.hook(False)
+        else:
+            self._gemm(self.da, self.gq_c.data, self.gq_c.inv_scale, wq[3].data_t, wq[3].inv_scale_t)
+            # relu^2 backward as a prologue of the quantizer: dh = bf16(h > 0 ? dA * 2h : 0)
+            out, out_t = nc.mx_outs(self.gq_4c)
+            if self.qhook:
+                self.qhook(True)
+            nc.check(nc.lib.mxb200_quantize_mx_relu_square_bwd(self.da.data_ptr(), self.h[l].data_ptr(), self.da.size(0),
+                                                               self.da.size(1), out, out_t, nc.SCALE_REFERENCE,
+                                                               torch.cuda.current_stream().cuda_stream), "quantize dh")
+            if self.qhook:
+                self.qhook(False)
         self._gemm(b.matrix(l, 3), self.gq_c.data_t, self.gq_c.inv_scale_t, self.aq[l].data_t, self.aq[l].inv_scale_t)
-        # relu^2 backward fused into the quantizer: dh = bf16(h > 0 ? dA * 2h : 0)
-        out, out_t = nc.mx_outs(self.gq_4c)
-        nc.check(nc.lib.mxb200_quantize_mx_relu_square_bwd(self.da.data_ptr(), self.h[l].data_ptr(), self.da.size(0),
-                                                           self.da.size(1), out, out_t, nc.SCALE_REFERENCE,
-                                                           torch.cuda.current_stream().cuda_stream), "quantize dh")
         self._gemm(self.dx, self.gq_4c.data, self.gq_4c.inv_scale, wq[2].data_t, wq[2].inv_scale_t)
         self._gemm(b.matrix(l, 2), self.gq_4c.data_t, self.gq_4c.inv_scale_t, self.xq_mlp[l].data_t, self.xq_mlp[l].inv_scale_t)
         # attention out
@@ -233,8 +281,8 @@ class DpStep:
             xs = self.xq_lm.inv_scale[begin * K // 32:(begin + rows) * K // 32]
             self._gemm(self.logits, xa, xs, self.wq_lm.data, self.wq_lm.inv_scale)
             g = self.dlogits[c % len(self.dlogits)]
-            nc.quantize_mx_into(g, False, nc.mx_out(self.gq_lm.data, self.gq_lm.inv_scale, begin, 0),
-                                nc.mx_out(self.gq_lm.data_t, self.gq_lm.inv_scale_t, 0, begin))
+            self._quant_into(g, False, nc.mx_out(self.gq_lm.data, self.gq_lm.inv_scale, begin, 0),
+                             nc.mx_out(self.gq_lm.data_t, self.gq_lm.inv_scale_t, 0, begin))
             ga = self.gq_lm.data[begin:begin + rows]
             gs = self.gq_lm.inv_scale[begin * cfg.vocab // 32:(begin + rows) * cfg.vocab // 32]
             self._gemm(self.dx_lm[begin:begin + rows], ga, gs, self.wq_lm.data_t, self.wq_lm.inv_scale_t)

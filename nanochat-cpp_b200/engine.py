@@ -19,7 +19,7 @@ __all__ = [
     "Fp8Tensor", "Fp8WeightCache", "MxGemmBackend", "set_mx_gemm_backend", "mx_gemm_backend", "mx_fits",
     "empty_mx", "empty_mx_scale", "mx_out", "mx_outs", "quantize_mx", "quantize_mx_into",
     "quantize_mx_relu_square_bwd", "quantize_fp8_weight", "mx_qkv_weights", "mx_gemm", "mx_gemm_out",
-    "mx_gemm_f32", "mx_grad_direct", "mx_grad_weights", "fp8_matmul", "fp8_eligible",
+    "mx_gemm_f32", "mx_gemm_relu_square", "mx_gemm_relu_square_bwd", "mx_grad_direct", "mx_grad_weights", "fp8_matmul", "fp8_eligible",
     "SCALE_REFERENCE", "SCALE_OCP_FLOOR",
 ]
 
@@ -286,6 +286,46 @@ def mx_gemm_f32(a: torch.Tensor, a_scale: torch.Tensor, b: torch.Tensor, b_scale
                                     capi.OUT_F32, None, M, N, K, ap, int(accumulate), s, ws.data_ptr(), ws.numel(),
                                     _stream())
     check(st, "mx_gemm_f32")
+
+
+def _check_mx_out(t: torch.Tensor, scale: torch.Tensor, rows: int, cols: int, what: str) -> None:
+    """src/nanochat/model/fp8/mx_gemm.cpp:125-130."""
+    if not (t.is_cuda and t.is_contiguous() and t.dtype == E4M3 and t.size(0) == rows and t.size(1) == cols
+            and scale.numel() == rows * cols // 32):
+        raise RuntimeError(f"{what}: expected e4m3 ({rows}, {cols}) with its MX scales")
+
+
+def mx_gemm_relu_square(h: torch.Tensor, q: torch.Tensor, q_scale: torch.Tensor, q_t: torch.Tensor,
+                        q_t_scale: torch.Tensor, a: torch.Tensor, a_scale: torch.Tensor, b: torch.Tensor,
+                        b_scale: torch.Tensor) -> bool:
+    """h = mx_gemm(a, ..., bf16) into h and q = quantize_mx(h, True, True, True) into q, q_t (N, M) in one GEMM
+    (src/nanochat/model/fp8/mx_gemm.h:29-35, mx_gemm.cpp:175-192). Returns True, as the reference does when its
+    fused backend applies; there is no unfused fallback to report here."""
+    M, N, K = _check_operands(a, a_scale, b, b_scale, "mx_gemm_relu_square")
+    if not (h.is_cuda and h.is_contiguous() and h.dtype == torch.bfloat16 and h.size(0) == M and h.size(1) == N):
+        raise RuntimeError("mx_gemm_relu_square: shape mismatch")
+    _check_mx_out(q, q_scale, M, N, "mx_gemm_relu_square")
+    _check_mx_out(q_t, q_t_scale, N, M, "mx_gemm_relu_square")
+    check(lib.mxb200_gemm_relu_square(a.data_ptr(), a_scale.data_ptr(), b.data_ptr(), b_scale.data_ptr(), h.data_ptr(),
+                                      q.data_ptr(), q_scale.data_ptr(), q_t.data_ptr(), q_t_scale.data_ptr(), M, N, K,
+                                      _stream()), "mx_gemm_relu_square")
+    return True
+
+
+def mx_gemm_relu_square_bwd(a: torch.Tensor, a_scale: torch.Tensor, b: torch.Tensor, b_scale: torch.Tensor,
+                            h: torch.Tensor, dh: torch.Tensor, dh_scale: torch.Tensor, dh_t: torch.Tensor,
+                            dh_t_scale: torch.Tensor) -> bool:
+    """relu^2's backward from its dgrad GEMM in one GEMM: ga = mx_gemm(a, ..., bf16) (not written) and h (M, N) bf16
+    -> quantize_mx_relu_square_bwd's outputs (src/nanochat/model/fp8/mx_gemm.h:37-42, mx_gemm.cpp:194-212)."""
+    M, N, K = _check_operands(a, a_scale, b, b_scale, "mx_gemm_relu_square_bwd")
+    if not (h.is_cuda and h.is_contiguous() and h.dtype == torch.bfloat16 and h.size(0) == M and h.size(1) == N):
+        raise RuntimeError("mx_gemm_relu_square_bwd: shape mismatch")
+    _check_mx_out(dh, dh_scale, M, N, "mx_gemm_relu_square_bwd")
+    _check_mx_out(dh_t, dh_t_scale, N, M, "mx_gemm_relu_square_bwd")
+    check(lib.mxb200_gemm_relu_square_bwd(a.data_ptr(), a_scale.data_ptr(), b.data_ptr(), b_scale.data_ptr(),
+                                          h.data_ptr(), dh.data_ptr(), dh_scale.data_ptr(), dh_t.data_ptr(),
+                                          dh_t_scale.data_ptr(), M, N, K, _stream()), "mx_gemm_relu_square_bwd")
+    return True
 
 
 # ------------------------------------------------------------------------------------------------ Linear

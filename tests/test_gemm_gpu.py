@@ -250,3 +250,53 @@ def test_argument_errors():
                                   out.data_ptr(), 0, None, 128, 128, K, None, 0, 2, None, 0, s) == nc.capi.ERR_WORKSPACE
     with pytest.raises(RuntimeError):
         nc.mx_gemm(qa.data, qa.inv_scale, qb.data[:, :512], qb.inv_scale, torch.bfloat16)
+
+
+# tests/test_fp8.cpp:368-369, plus a tile-crossing shape with M % 256 == 128 and one of BASELINE's MLP size class
+FUSED_SHAPES = [(128, 128, 128), (256, 384, 512), (640, 512, 1536), (2048, 6144, 1536)]
+
+
+@pytest.mark.parametrize("M,N,K", FUSED_SHAPES)
+@pytest.mark.parametrize("tile_n", [0, 384, 512])
+def test_relu_square_gemm_matches_unfused(M, N, K, tile_n):
+    """Fp8.CutlassReluSquareGemmMatchesUnfused (tests/test_fp8.cpp:363-390): the fc GEMM with relu^2's MX quantize
+    in the epilogue vs the GEMM then quantize_mx, bit for bit."""
+    nc.capi.lib.mxb200_set_gemm_config(tile_n, 0)
+    qa, qb = quantized(M, N, K, seed=12)
+    want_h = nc.mx_gemm(qa.data, qa.inv_scale, qb.data, qb.inv_scale, torch.bfloat16)
+    want = nc.quantize_mx(want_h, True, True, True)
+    h = torch.full_like(want_h, float("nan"))
+    got = nc.empty_mx(M, N, h.device)
+    for t in (got.data, got.data_t, got.inv_scale, got.inv_scale_t):
+        t.view(torch.uint8).zero_()
+    assert nc.mx_gemm_relu_square(h, got.data, got.inv_scale, got.data_t, got.inv_scale_t, qa.data, qa.inv_scale,
+                                  qb.data, qb.inv_scale)
+    assert torch.equal(h, want_h)
+    for name in ("data", "inv_scale", "data_t", "inv_scale_t"):
+        g, w = getattr(got, name).view(torch.uint8), getattr(want, name).view(torch.uint8)
+        assert torch.equal(g, w), f"{name}: {(g != w).sum().item()} bytes differ"
+    # and against the CPU oracle end to end on the small shapes
+    if M * N <= 640 * 512:
+        ref = mo.quantize_mx(np_f32(want_h), True, True, mo.PROLOGUE_RELU_SQUARE)
+        assert np.array_equal(np_u8(got.data), ref["data"]) and np.array_equal(np_u8(got.inv_scale_t), ref["scale_t"])
+
+
+@pytest.mark.parametrize("M,N,K", FUSED_SHAPES)
+@pytest.mark.parametrize("tile_n", [0, 384, 512])
+def test_relu_square_bwd_gemm_matches_unfused(M, N, K, tile_n):
+    """Fp8.CutlassReluSquareBwdGemmMatchesUnfused (tests/test_fp8.cpp:394-426): the proj dgrad GEMM with relu^2's
+    backward quantize in the epilogue vs the GEMM then quantize_mx_relu_square_bwd, bit for bit."""
+    nc.capi.lib.mxb200_set_gemm_config(tile_n, 0)
+    qa, qb = quantized(M, N, K, seed=13)
+    g = torch.Generator().manual_seed(14)
+    h = torch.randn(M, N, generator=g).to(torch.bfloat16).cuda()
+    ga = nc.mx_gemm(qa.data, qa.inv_scale, qb.data, qb.inv_scale, torch.bfloat16)
+    want = nc.quantize_mx_relu_square_bwd(ga, h)
+    got = nc.empty_mx(M, N, h.device)
+    for t in (got.data, got.data_t, got.inv_scale, got.inv_scale_t):
+        t.view(torch.uint8).zero_()
+    assert nc.mx_gemm_relu_square_bwd(qa.data, qa.inv_scale, qb.data, qb.inv_scale, h, got.data, got.inv_scale,
+                                      got.data_t, got.inv_scale_t)
+    for name in ("data", "inv_scale", "data_t", "inv_scale_t"):
+        gt, w = getattr(got, name).view(torch.uint8), getattr(want, name).view(torch.uint8)
+        assert torch.equal(gt, w), f"{name}: {(gt != w).sum().item()} bytes differ"
