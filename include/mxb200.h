@@ -73,6 +73,35 @@ MXB200_API int mxb200_quantize_mx(const void* x, int x_bf16, int64_t rows, int64
 MXB200_API int mxb200_quantize_mx_relu_square_bwd(const void* g, const void* h, int64_t rows, int64_t cols, mxb200_mx_out out,
                                        mxb200_mx_out out_t, int scale_rule, void* stream);
 
+/* Arguments of mxb200_residual_norm_mx_fwd; the fields of nanochat::kernels::ResidualNormMxFwd and its base
+ * ResidualNormFwd (src/nanochat/model/ops/residual_norm_kernel.h:17-41) in one flat struct. All tensors are
+ * (rows, cols) contiguous bf16 unless noted, 16-byte aligned. */
+typedef struct mxb200_residual_norm_mx {
+  const void* x;    /* the residual stream */
+  const void* r;    /* added to x first (the previous block's output); null: no add */
+  const void* x0;   /* blended in with the layer's lambdas; null: no blend */
+  const float* lr;  /* device fp32 scalars, required with x0 */
+  const float* l0;
+  void* s;          /* out, optional: bf16(x + r), kept for the lambdas' gradients when both r and x0 are given */
+  void* res;        /* out: the new residual stream */
+  void* n;          /* out, (rows, cols): only columns [0, n_cols) of the normalized rows are written, rounded up to
+                       whole 8-column vectors (the value-embedding gate reads them); may be null when n_cols == 0 */
+  float* rstd;      /* out: (rows) fp32 reciprocal RMS per row */
+  int64_t rows;
+  int32_t cols;
+  float eps;
+  mxb200_mx_out out;   /* MX of n: (rows, cols) scaled along rows */
+  mxb200_mx_out out_t; /* MX of n^T: (cols, rows) */
+  int32_t n_cols;
+} mxb200_residual_norm_mx;
+
+/* Replaces nanochat::kernels::residual_norm_mx_fwd (src/nanochat/model/ops/residual_norm_kernel.h:28-41, kernels
+ * nanochat_residual_norm_mx_fwd_c*, residual_norm_kernel.cu:153-214): per row s = bf16(x + r),
+ * res = bf16(bf16(lr * s) + bf16(l0 * x0)), n = bf16(res * rsqrt(mean(res^2) + eps)), and n leaves MX-quantized in
+ * both layouts instead of being written, bit for bit what mxb200_quantize_mx of the bf16 n would give. It is the
+ * producer of the quantized input of the QKV and MLP-fc GEMMs. rows, cols % 128 == 0, cols <= 2048. */
+MXB200_API int mxb200_residual_norm_mx_fwd(const mxb200_residual_norm_mx* args, void* stream);
+
 /* Replaces nanochat::kernels::cutlass_mx_gemm_bf16 (src/nanochat/model/fp8/mx_gemm_kernel.h:13-17).
  * d (M, N) bf16 row-major = a (M, K) . b (N, K)^T; a, b row-major e4m3 with their swizzled e8m0 scales along K;
  * fp32 accumulation, one round-to-nearest-even to bf16. M, N, K % 128 == 0, pointers 16-byte aligned.

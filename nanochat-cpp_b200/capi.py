@@ -21,7 +21,7 @@ STATIC_SCRATCH_BYTES = 32 << 20
 # every symbol include/mxb200.h declares
 SYMBOLS = (
     "mxb200_quantize_mx", "mxb200_quantize_mx_relu_square_bwd", "mxb200_gemm_bf16", "mxb200_gemm_f32",
-    "mxb200_gemm_relu_square", "mxb200_gemm_relu_square_bwd",
+    "mxb200_gemm_relu_square", "mxb200_gemm_relu_square_bwd", "mxb200_residual_norm_mx_fwd",
     "mxb200_gemm_splits", "mxb200_gemm_workspace_bytes", "mxb200_gemm_splitk", "mxb200_gemm_splitk_static",
     "mxb200_strerror",
     "mxb200_device_status", "mxb200_set_gemm_config", "mxb200_launch_count", "mxb200_version",
@@ -32,6 +32,14 @@ class MxOut(ctypes.Structure):
     """mxb200_mx_out / nanochat::kernels::MxOut."""
     _fields_ = [("data", ctypes.c_void_p), ("ld", ctypes.c_int64), ("scale", ctypes.c_void_p),
                 ("scale_tiles", ctypes.c_int64)]
+
+
+class ResidualNormMx(ctypes.Structure):
+    """mxb200_residual_norm_mx."""
+    _fields_ = [("x", ctypes.c_void_p), ("r", ctypes.c_void_p), ("x0", ctypes.c_void_p), ("lr", ctypes.c_void_p),
+                ("l0", ctypes.c_void_p), ("s", ctypes.c_void_p), ("res", ctypes.c_void_p), ("n", ctypes.c_void_p),
+                ("rstd", ctypes.c_void_p), ("rows", ctypes.c_int64), ("cols", ctypes.c_int32), ("eps", ctypes.c_float),
+                ("out", MxOut), ("out_t", MxOut), ("n_cols", ctypes.c_int32)]
 
 
 class Mxb200Error(RuntimeError):
@@ -52,6 +60,7 @@ def _load() -> ctypes.CDLL:
     lib.mxb200_gemm_f32.argtypes = [vp, vp, vp, vp, vp, i64, i64, i64, vp, i32, vp]
     lib.mxb200_gemm_relu_square.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, i64, i64, i64, vp]
     lib.mxb200_gemm_relu_square_bwd.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, i64, i64, i64, vp]
+    lib.mxb200_residual_norm_mx_fwd.argtypes = [ctypes.POINTER(ResidualNormMx), vp]
     lib.mxb200_gemm_splits.argtypes = [i64, i64, i64]
     lib.mxb200_gemm_workspace_bytes.argtypes = [i64, i64, i64, i32]
     lib.mxb200_gemm_workspace_bytes.restype = ctypes.c_size_t

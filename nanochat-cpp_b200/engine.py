@@ -18,7 +18,7 @@ from .capi import MxOut, check, lib
 __all__ = [
     "Fp8Tensor", "Fp8WeightCache", "MxGemmBackend", "set_mx_gemm_backend", "mx_gemm_backend", "mx_fits",
     "empty_mx", "empty_mx_scale", "mx_out", "mx_outs", "quantize_mx", "quantize_mx_into",
-    "quantize_mx_relu_square_bwd", "quantize_fp8_weight", "mx_qkv_weights", "mx_gemm", "mx_gemm_out",
+    "quantize_mx_relu_square_bwd", "residual_norm_mx", "residual_norm_mx_fits", "quantize_fp8_weight", "mx_qkv_weights", "mx_gemm", "mx_gemm_out",
     "mx_gemm_f32", "mx_gemm_relu_square", "mx_gemm_relu_square_bwd", "mx_grad_direct", "mx_grad_weights", "fp8_matmul", "fp8_eligible",
     "SCALE_REFERENCE", "SCALE_OCP_FLOOR",
 ]
@@ -149,6 +149,48 @@ def quantize_mx_relu_square_bwd(g: torch.Tensor, h: torch.Tensor, rows: bool = T
     check(lib.mxb200_quantize_mx_relu_square_bwd(g.data_ptr(), h.data_ptr(), g.size(0), g.size(1), out, out_t,
                                                  scale_rule, _stream()), "quantize_mx_relu_square_bwd")
     return q
+
+
+def residual_norm_mx_fits(rows: int, cols: int) -> bool:
+    """Whether residual_norm_mx handles (rows, cols): both % 128 and cols within the kernel's row-in-registers limit
+    (the reference's is 1536, src/nanochat/model/ops/residual_norm_kernel.h:15; this kernel's is 2048)."""
+    return mx_fits(rows, cols) and cols <= 2048
+
+
+def residual_norm_mx(x: torch.Tensor, r: Optional[torch.Tensor] = None, x0: Optional[torch.Tensor] = None,
+                     lr: Optional[torch.Tensor] = None, l0: Optional[torch.Tensor] = None, layer: int = 0,
+                     gate_cols: int = 0, eps: float = torch.finfo(torch.float32).eps):
+    """Forward of the reference's fused residual step with MX output (src/nanochat/model/ops/residual_norm.cpp:36-96,
+    the `mx` branch): s = x + r, res = lr[layer] * s + l0[layer] * x0 (with the op path's bf16 roundings),
+    n = rms_norm(res). Returns (res, n, n_mx, rstd, s): n holds only its first gate_cols columns; n_mx is
+    quantize_mx(n) in both layouts, bit for bit; s is None unless both r and x0 are given."""
+    _require_cuda(x, "residual_norm_mx")
+    cols = x.size(-1)
+    rows = x.numel() // cols
+    if not (x.dtype == torch.bfloat16 and x.is_contiguous() and residual_norm_mx_fits(rows, cols)
+            and 0 <= gate_cols <= cols):
+        raise RuntimeError("residual_norm_mx: shape")
+    for t in (r, x0):
+        if t is not None and not (t.dtype == torch.bfloat16 and t.is_contiguous() and t.shape == x.shape):
+            raise RuntimeError("residual_norm_mx: expected contiguous bf16 of x's shape")
+    blend = x0 is not None
+    if blend and not (lr is not None and l0 is not None and lr.dtype == l0.dtype == torch.float32
+                      and 0 <= layer < lr.numel() == l0.numel() and lr.is_contiguous() and l0.is_contiguous()):
+        raise RuntimeError("residual_norm_mx: the blend needs fp32 lambdas")
+    res = torch.empty_like(x)
+    n = torch.empty_like(x)
+    rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
+    s = torch.empty_like(x) if (r is not None and blend) else None
+    n_mx = empty_mx(rows, cols, x.device)
+    out, out_t = mx_outs(n_mx)
+    args = capi.ResidualNormMx(x.data_ptr(), r.data_ptr() if r is not None else None,
+                               x0.data_ptr() if blend else None,
+                               lr.data_ptr() + 4 * layer if blend else None, l0.data_ptr() + 4 * layer if blend else None,
+                               s.data_ptr() if s is not None else None, res.data_ptr(), n.data_ptr(), rstd.data_ptr(),
+                               rows, cols, eps, out, out_t, gate_cols)
+    import ctypes
+    check(lib.mxb200_residual_norm_mx_fwd(ctypes.byref(args), _stream()), "residual_norm_mx")
+    return res, n, n_mx, rstd, s
 
 
 class Fp8WeightCache:

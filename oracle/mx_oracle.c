@@ -136,3 +136,47 @@ float mxo_bf16_out(float acc, int has_resid, float resid) {
   if (has_resid) o = mxo_round_bf16(o + resid);
   return o;
 }
+
+/* Fused residual add + lambda blend + RMS norm, one row at a time
+ * (src/nanochat/model/ops/residual_norm_kernel.cu:80-128). Inputs and outputs are fp32 arrays holding bf16 values:
+ *   s = r ? bf16(x + r) : x;  res = x0 ? bf16(bf16(lr_b * s) + bf16(l0_b * x0)) : s   (lr_b, l0_b = bf16 of the lambdas)
+ *   rstd = 1 / sqrt(sum(res^2) / cols + eps);  n = bf16(res * rstd)
+ * The sum of squares follows the kernel's order: 32 lanes, lane l accumulating columns (it * 32 + l) * 8 .. + 7 for
+ * it = 0, 1, ... in fp32 (a bf16 square is exact in fp32, so fused and unfused multiply-add agree), then the
+ * xor 16-8-4-2-1 butterfly, after which every lane holds the same total. The device's rsqrt is approximate, so a
+ * caller that wants n bit for bit passes the device's rstd in rstd_in (null: computed here in double).
+ * r, x0, s, n may be null. */
+void mxo_residual_norm(const float* x, const float* r, const float* x0, float lr, float l0, int64_t rows, int cols,
+                       float eps, const float* rstd_in, float* s, float* res, float* rstd, float* n) {
+  const float lr_b = mxo_round_bf16(lr), l0_b = mxo_round_bf16(l0);
+  for (int64_t row = 0; row < rows; ++row) {
+    float lane_sum[32];
+    for (int l = 0; l < 32; ++l) lane_sum[l] = 0.f;
+    for (int it = 0; it * 256 < cols; ++it)
+      for (int l = 0; l < 32; ++l) {
+        const int col = (it * 32 + l) * 8;
+        if (col >= cols) break;
+        for (int k = 0; k < 8; ++k) {
+          const int64_t i = row * cols + col + k;
+          float v = x[i];
+          if (r) {
+            v = mxo_round_bf16(v + r[i]);
+            if (s) s[i] = v;
+          }
+          if (x0) v = mxo_round_bf16(mxo_round_bf16(lr_b * v) + mxo_round_bf16(l0_b * x0[i]));
+          res[i] = v;
+          lane_sum[l] = v * v + lane_sum[l];
+        }
+      }
+    for (int o = 16; o > 0; o >>= 1) {
+      float next[32];
+      for (int l = 0; l < 32; ++l) next[l] = lane_sum[l] + lane_sum[l ^ o];
+      for (int l = 0; l < 32; ++l) lane_sum[l] = next[l];
+    }
+    const float mean = lane_sum[0] / (float)cols + eps;
+    const float rs = rstd_in ? rstd_in[row] : (float)(1.0 / sqrt((double)mean));
+    rstd[row] = rs;
+    if (n)
+      for (int c = 0; c < cols; ++c) n[row * cols + c] = mxo_round_bf16(res[row * cols + c] * rs);
+  }
+}

@@ -237,6 +237,44 @@ def gemm_f32_out(acc, alpha: float = 1.0, d_old=None) -> np.ndarray:
     return out
 
 
+def residual_norm(x, r=None, x0=None, lr: float = 1.0, l0: float = 0.0, eps: float = 1e-6, rstd=None):
+    """Fused residual add + lambda blend + RMS norm over rows of bf16 values held as fp32
+    (src/nanochat/model/ops/residual_norm_kernel.cu:80-128):
+      s = r ? bf16(x + r) : x;  res = x0 ? bf16(bf16(lr_b * s) + bf16(l0_b * x0)) : s;  n = bf16(res * rstd)
+    The sum of squares is taken in the kernel's order (lane l of 32 owns columns (it * 32 + l) * 8 .. + 7, fp32
+    accumulation in column order, then the xor 16..1 butterfly); a bf16 square is exact in fp32, so the kernel's
+    fused multiply-add and a plain add agree. rstd given: used as is (the device's rsqrt is approximate).
+    Returns (s, res, rstd, n); s is None without r."""
+    x = np.asarray(x, dtype=np.float32)
+    rows, cols = x.shape
+    s = None
+    v = x
+    if r is not None:
+        v = round_bf16(x + np.asarray(r, dtype=np.float32))
+        s = v
+    if x0 is not None:
+        lr_b, l0_b = round_bf16(np.float32(lr)), round_bf16(np.float32(l0))
+        v = round_bf16(round_bf16(lr_b * v) + round_bf16(l0_b * np.asarray(x0, dtype=np.float32)))
+    res = v
+    iters = (cols + 255) // 256
+    padded = np.zeros((rows, iters * 256), dtype=np.float32)
+    padded[:, :cols] = res
+    sq = (padded * padded).reshape(rows, iters, 32, 8)      # [row, it, lane, k]: exact products
+    lanes = np.zeros((rows, 32), dtype=np.float32)
+    for it in range(iters):
+        for k in range(8):
+            lanes = (lanes + sq[:, it, :, k]).astype(np.float32)
+    idx = np.arange(32)
+    for o in (16, 8, 4, 2, 1):
+        lanes = (lanes + lanes[:, idx ^ o]).astype(np.float32)
+    mean = (lanes[:, 0] / np.float32(cols) + np.float32(eps)).astype(np.float32)
+    if rstd is None:
+        rstd = (1.0 / np.sqrt(mean.astype(np.float64))).astype(np.float32)
+    rstd = np.asarray(rstd, dtype=np.float32)
+    n = round_bf16(res * rstd[:, None])
+    return s, res, rstd, n
+
+
 def rel_norm_diff(a, b) -> float:
     """||a - b|| / ||b|| in fp64 (tests/test_fp8.cpp:20-23)."""
     a64, b64 = np.asarray(a, dtype=np.float64), np.asarray(b, dtype=np.float64)

@@ -6,7 +6,10 @@ quantize_*.npz: a seeded CPU-drawn input and the bytes the reference's OWN CUDA 
 (nanochat_mx_quantize_* of src/nanochat/model/fp8/fp8_kernel.cu, compiled unmodified by oracle/Makefile into
 oracle/_ref/) wrote for it on the GPU, both layouts. gemm_*.npz: quantized operands and the fp32 result of
 cuBLASLt's MXFP8 GEMM (torch._scaled_mm, the arithmetic of the reference's --gemm=cublas backend,
-src/nanochat/model/fp8/mx_gemm.cpp:158). The CPU test suite checks the oracle against these files.
+src/nanochat/model/fp8/mx_gemm.cpp:158). residual_norm_*.npz: seeded inputs of the fused residual step and what the
+reference's own nanochat_residual_norm_mx_fwd_c* / nanochat_residual_norm_fwd_c* kernels
+(src/nanochat/model/ops/residual_norm_kernel.cu, compiled unmodified) wrote for them: s, res, rstd, the MX bytes of n in
+both layouts, and n itself from the plain kernel. The CPU test suite checks the oracle against these files.
 """
 import os
 import sys
@@ -20,7 +23,7 @@ sys.path.insert(0, ROOT)
 sys.path.insert(0, os.path.join(ROOT, "tests"))
 
 import refkernel  # noqa: E402
-from helpers import gemm_operands, quantizer_input  # noqa: E402
+from helpers import gemm_operands, quantizer_input, residual_norm_inputs  # noqa: E402
 
 
 def bits(t):
@@ -52,6 +55,27 @@ def main():
         rec.update(data=data.cpu().numpy(), scale=scale.cpu().numpy(), data_t=data_t.cpu().numpy(), scale_t=scale_t.cpu().numpy())
         np.savez_compressed(os.path.join(out, f"quantize_{name}.npz"), **rec)
         print("wrote", name)
+    for R, C, add, blend in [(128, 256, True, True), (128, 384, True, False), (128, 128, False, False)]:
+        inp = residual_norm_inputs(R, C, add, blend, seed=21)
+        c = lambda t: None if t is None else t.cuda()
+        args = (c(inp["x"]), c(inp["r"]), c(inp["x0"]), c(inp["lr"]), c(inp["l0"]), inp["layer"])
+        mx = refkernel.residual_norm(*args, gate_cols=0, mx=True)
+        plain = refkernel.residual_norm(*args, mx=False)
+        torch.cuda.synchronize()
+        assert torch.equal(mx["res"], plain["res"]) and torch.equal(mx["rstd"], plain["rstd"])
+        rec = {"x_bf16_bits": bits(inp["x"]), "eps": np.float32(torch.finfo(torch.float32).eps),
+               "lr": np.float32(inp["lr"][inp["layer"]] if blend else 1), "l0": np.float32(inp["l0"][inp["layer"]] if blend else 0),
+               "res_bf16_bits": bits(mx["res"].cpu()), "n_bf16_bits": bits(plain["n"].cpu()), "rstd": mx["rstd"].cpu().numpy()}
+        if add:
+            rec["r_bf16_bits"] = bits(inp["r"])
+        if blend:
+            rec["x0_bf16_bits"] = bits(inp["x0"])
+        if mx["s"] is not None:
+            rec["s_bf16_bits"] = bits(mx["s"].cpu())
+        rec.update({k: mx[k].cpu().numpy() for k in ("data", "scale", "data_t", "scale_t")})
+        name = f"{R}x{C}" + ("_add" if add else "") + ("_blend" if blend else "")
+        np.savez_compressed(os.path.join(out, f"residual_norm_{name}.npz"), **rec)
+        print("wrote residual_norm", name)
     for M, N, K in [(128, 128, 128), (256, 384, 512)]:
         a, b = gemm_operands(M, N, K)
         qa = refkernel.quantize_mx(a.cuda())

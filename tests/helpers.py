@@ -49,3 +49,17 @@ def assert_quantized_equal(q, want: dict, what: str = ""):
         w = want[key].reshape(-1)
         bad = int((g != w).sum())
         assert bad == 0, f"{what} {key}: {bad} of {g.size} bytes differ (first at {int(np.argmax(g != w))})"
+
+
+def residual_norm_inputs(rows: int, cols: int, add: bool, blend: bool, seed: int = 0) -> dict:
+    """Inputs of the fused residual step as nanochat-cpp's test draws them (tests/test_residual_norm.cpp:80-97):
+    unit-normal bf16 x whose first row is scaled by 1e-4 (a tiny row, where eps matters), r at half that spread,
+    five fp32 lambdas per kind, lr in [0.5, 1.5) and l0 in [0, 0.3), layer 3. CPU tensors."""
+    g = torch.Generator().manual_seed(seed + 7 * rows + cols)
+    x = torch.randn(rows, cols, generator=g).to(torch.bfloat16)
+    x[0] = (x[0].float() * 1e-4).to(torch.bfloat16)
+    r = (torch.randn(rows, cols, generator=g) * 0.5).to(torch.bfloat16) if add else None
+    x0 = torch.randn(rows, cols, generator=g).to(torch.bfloat16) if blend else None
+    lr = (torch.rand(5, generator=g) + 0.5) if blend else None
+    l0 = (torch.rand(5, generator=g) * 0.3) if blend else None
+    return {"x": x, "r": r, "x0": x0, "lr": lr, "l0": l0, "layer": 3}

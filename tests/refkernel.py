@@ -47,3 +47,45 @@ def quantize_mx(x: torch.Tensor, relu_square: bool = False, h: torch.Tensor | No
                                                     scale_t.data_ptr(), R // 128, stream)
     assert err == 0, f"reference kernel launch failed: cudaError {err}"
     return data, scale, data_t, scale_t
+
+
+def _bind_residual_norm(l):
+    vp, i64, i32, f32 = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int, ctypes.c_float
+    l.ref_residual_norm_fwd.argtypes = [vp] * 9 + [i64, i32, f32, vp]
+    l.ref_residual_norm_mx_fwd.argtypes = [vp] * 9 + [i64, i32, f32, vp, i64, vp, i64, vp, i64, vp, i64, i32, vp]
+
+
+def residual_norm(x, r=None, x0=None, lr=None, l0=None, layer=0, gate_cols=0, mx=True,
+                  eps=float(torch.finfo(torch.float32).eps)):
+    """Runs nanochat::kernels::residual_norm_mx_fwd (mx) or residual_norm_fwd on the GPU. Returns a dict of
+    res, s (None unless r and x0), rstd, n (bf16, full width: only the first gate_cols columns are written with mx)
+    and, with mx, data / scale / data_t / scale_t."""
+    l = lib()
+    if not hasattr(l, "_rn_bound"):
+        _bind_residual_norm(l)
+        l._rn_bound = True
+    R, C = x.shape
+    dev = x.device
+    blend = x0 is not None
+    res = torch.zeros_like(x)
+    n = torch.zeros_like(x)
+    s = torch.zeros_like(x) if (r is not None and blend) else None
+    rstd = torch.zeros(R, dtype=torch.float32, device=dev)
+    ptr = lambda t: t.data_ptr() if t is not None else None
+    lam = lambda t: t.data_ptr() + 4 * layer if blend else None
+    stream = torch.cuda.current_stream().cuda_stream
+    base = [x.data_ptr(), ptr(r), ptr(x0), lam(lr), lam(l0), ptr(s), res.data_ptr(), n.data_ptr(), rstd.data_ptr(),
+            R, C, eps]
+    out = {"res": res, "s": s, "rstd": rstd, "n": n}
+    if mx:
+        data = torch.zeros((R, C), dtype=torch.uint8, device=dev)
+        data_t = torch.zeros((C, R), dtype=torch.uint8, device=dev)
+        scale = torch.zeros(R * C // 32, dtype=torch.uint8, device=dev)
+        scale_t = torch.zeros(R * C // 32, dtype=torch.uint8, device=dev)
+        err = l.ref_residual_norm_mx_fwd(*base, data.data_ptr(), C, scale.data_ptr(), C // 128, data_t.data_ptr(), R,
+                                         scale_t.data_ptr(), R // 128, gate_cols, stream)
+        out.update(data=data, scale=scale, data_t=data_t, scale_t=scale_t)
+    else:
+        err = l.ref_residual_norm_fwd(*base, stream)
+    assert err == 0, f"reference kernel launch failed: {err}"
+    return out

@@ -8,7 +8,7 @@ import numpy as np
 import pytest
 import torch
 
-from helpers import quantizer_input, gemm_operands, np_f32, np_u8
+from helpers import quantizer_input, gemm_operands, np_f32, np_u8, residual_norm_inputs
 from oracle import mx_oracle as mo
 from oracle import torch_reference as tr
 
@@ -148,3 +148,74 @@ def test_gemm_oracle_matches_cublaslt_golden(path):
     g = np.load(path)
     ref = mo.mx_gemm_ref(g["a"], g["a_scale"], g["b"], g["b_scale"])
     assert mo.rel_norm_diff(ref, g["d_f32"]) < 1e-5
+
+
+# ---------------------------------------------------------------- fused residual step
+
+RN_CASES = [(128, 768, True, True), (128, 256, False, False), (64, 1536, True, False), (32, 2048, False, True),
+            (5, 136, True, True), (3, 24, True, True)]  # the last two: partial warp passes (tests/test_residual_norm.cpp:98)
+
+
+def _rn_args(rows, cols, add, blend):
+    inp = residual_norm_inputs(rows, cols, add, blend)
+    f = lambda t: None if t is None else np.ascontiguousarray(np_f32(t))
+    lr, l0 = (float(inp["lr"][inp["layer"]]), float(inp["l0"][inp["layer"]])) if blend else (1.0, 0.0)
+    return inp, f(inp["x"]), f(inp["r"]), f(inp["x0"]), lr, l0, float(np.finfo(np.float32).eps)
+
+
+@pytest.mark.parametrize("rows,cols,add,blend", RN_CASES)
+def test_residual_norm_numpy_matches_c(oracle_c, rows, cols, add, blend):
+    _, x, r, x0, lr, l0, eps = _rn_args(rows, cols, add, blend)
+    s, res, rstd, n = mo.residual_norm(x, r, x0, lr, l0, eps)
+    cs, cres, cn, crstd = np.zeros_like(x), np.zeros_like(x), np.zeros_like(x), np.zeros(rows, np.float32)
+    p = lambda a: None if a is None else a.ctypes.data
+    oracle_c.mxo_residual_norm(p(x), p(r), p(x0), lr, l0, rows, cols, eps, None, p(cs) if add else None, p(cres),
+                               p(crstd), p(cn))
+    assert np.array_equal(res, cres) and np.array_equal(rstd, crstd) and np.array_equal(n, cn)
+    assert s is None or np.array_equal(s, cs)
+
+
+@pytest.mark.parametrize("rows,cols,add,blend", RN_CASES)
+def test_residual_norm_matches_torch_ops(rows, cols, add, blend):
+    """The op-by-op bf16 path the fused kernel is checked against (tests/test_residual_norm.cpp:41-51), with the
+    lambdas rounded to bf16 as type promotion does on the device: res bit for bit, n within one bf16 rounding of
+    F.rms_norm."""
+    inp, x, r, x0, lr, l0, eps = _rn_args(rows, cols, add, blend)
+    s, res, rstd, n = mo.residual_norm(x, r, x0, lr, l0, eps)
+    ts = inp["x"] + inp["r"] if add else inp["x"]
+    tres = ts
+    if blend:
+        k = inp["layer"]
+        tres = inp["lr"][k].to(torch.bfloat16) * ts + inp["l0"][k].to(torch.bfloat16) * inp["x0"]
+    assert np.array_equal(np_f32(tres), res)
+    want = torch.nn.functional.rms_norm(tres.float(), (cols,), eps=eps).numpy()
+    assert np.all(np.abs(n - want) <= np.maximum(np.abs(want) * 2.0 ** -8, 1e-30))
+    ref_rstd = 1.0 / np.sqrt((res.astype(np.float64) ** 2).mean(axis=1) + eps)
+    assert np.allclose(rstd, ref_rstd, rtol=5e-7)
+
+
+def _rn_golden_files():
+    return sorted(glob.glob(os.path.join(GOLDEN, "residual_norm_*.npz")))
+
+
+@pytest.mark.parametrize("path", _rn_golden_files() or [None])
+def test_residual_norm_oracle_matches_reference_kernel_golden(path):
+    """What the reference's own nanochat_residual_norm_mx_fwd_c* kernel wrote on a B200 (tests/golden/make_golden.py):
+    s, res and the MX bytes bit for bit, n bit for bit given the kernel's rstd, rstd itself within the device
+    rsqrt's 2 ulp."""
+    if path is None:
+        pytest.skip("no golden files yet")
+    g = np.load(path)
+    f = lambda k: mo.bf16_bits_to_f32(g[k]) if k in g else None
+    x, r, x0 = f("x_bf16_bits"), f("r_bf16_bits"), f("x0_bf16_bits")
+    lr, l0, eps = float(g["lr"]), float(g["l0"]), float(g["eps"])
+    s, res, rstd, _ = mo.residual_norm(x, r, x0, lr, l0, eps)
+    assert np.array_equal(res, f("res_bf16_bits"))
+    if "s_bf16_bits" in g:
+        assert np.array_equal(s, f("s_bf16_bits"))
+    assert np.allclose(rstd, g["rstd"], rtol=3e-7, atol=0)
+    _, _, _, n = mo.residual_norm(x, r, x0, lr, l0, eps, rstd=g["rstd"])
+    assert np.array_equal(n, f("n_bf16_bits"))
+    want = mo.quantize_mx(n)
+    for key in ("data", "scale", "data_t", "scale_t"):
+        assert np.array_equal(want[key].reshape(-1), g[key].reshape(-1)), (os.path.basename(path), key)
