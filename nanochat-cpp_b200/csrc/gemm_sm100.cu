@@ -1547,6 +1547,8 @@ extern "C" int mxb200_device_status(uint32_t* word) {
     const uint32_t zero = 0;
     cudaMemcpyToSymbol(mxb200::g_watchdog_word, &zero, sizeof(zero));
   }
+  if (const uint32_t norm = mxb200::take_norm_watchdog_word(); w == 0)
+    w = norm;
   if (word != nullptr)
     *word = w;
   return w == 0 ? MXB200_OK : MXB200_ERR_WATCHDOG;

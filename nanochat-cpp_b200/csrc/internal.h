@@ -29,6 +29,9 @@ using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t
                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 EncodeTiledFn encode_fn();
 
+// The residual-norm kernel's watchdog word (non-zero after one of its bounded waits ran out), read and cleared.
+uint32_t take_norm_watchdog_word();
+
 inline bool aligned16(const void* p) {
   return (reinterpret_cast<uintptr_t>(p) & 15u) == 0;
 }

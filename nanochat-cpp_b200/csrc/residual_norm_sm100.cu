@@ -4,58 +4,115 @@
 // same bits. Per row of `cols` bf16 values:
 //   s = r ? bf16(x + r) : x;  res = x0 ? bf16(bf16(lr * s) + bf16(l0 * x0)) : s   (lr, l0 rounded to bf16 first)
 //   rstd = rsqrt(sum(res^2) / cols + eps);  n = bf16(res * rstd);  MX(n) row-wise and column-wise
-// The roundings are the reference's (residual_norm_kernel.cu:80-128). rstd is bit-exact only if the sum of squares
-// is taken in the reference's order, so that part is fixed: a warp owns a row, lane l owns columns
-// (it * 32 + l) * 8 .. + 7 for it = 0, 1, ..., accumulates them in order with fused multiply-adds, and the warp
-// combines with the xor-16-8-4-2-1 butterfly. Everything around it is laid out for HBM: every global access is a
-// 16- or 32-byte vector in a fully coalesced warp pattern, each input byte is read once and each output byte
-// written once (x, r, x0: 2 B each; res, s: 2 B each; MX: 2 x (1 + 1/32) B per element).
+// The roundings are the reference's (residual_norm_kernel.cu:80-128). A bf16 product is exact in fp32 and the fp32
+// sum of two bf16 values rounds to bf16 as the exact sum does, so the add and the blend run as packed bf16x2
+// instructions (add.rn / mul.rn, never contracted) with the same bits as the reference's fp32-then-round form.
+// rstd is bit-exact only if the sum of squares is taken in the reference's order, so that part is fixed: a warp owns
+// a row, lane l owns columns (it * 32 + l) * 8 .. + 7 for it = 0, 1, ..., accumulates them in order, and the warp
+// combines with the xor-16-8-4-2-1 butterfly.
 //
-// One CTA owns a tile of 32 rows (one scale block of the column-wise layout) x all columns, 8 warps x 4 rows each;
-// the bf16 n values are parked in shared memory for the column pass, in which a thread owns two adjacent columns
-// (packed 32-bit reads, conflict-free) and writes 32 contiguous bytes per transposed row.
+// Everything around that is laid out for HBM. A persistent CTA per SM owns tiles of 32 rows (one scale block of
+// the column-wise layout) x all columns. One producer warp streams the input rows of this and the following tiles
+// into a shared-memory ring with bulk async copies (one contiguous row of x, r, x0 per slot, completion on an
+// mbarrier), as far ahead as the ring is deep, so loads stay in flight while the 16 consumer warps compute, store
+// and run the column pass. A consumer warp takes a row from its slot, releases the slot after the first pass, parks
+// the bf16 n in a shared tile and writes res, s, rstd and the row-wise MX bytes; after all 32 rows, each thread owns
+// a column of the tile and writes 32 contiguous bytes of the transposed layout. Each input byte is read once and
+// each output byte written once (x, r, x0: 2 B each; res, s: 2 B each; MX: 2 x (1 + 1/32) B per element).
+// Every wait is bounded: after kWaitLimitNs it records its site in a device word, raises a CTA-wide flag that all
+// other waits poll, and the CTA returns once its copies in flight have landed.
+#include <algorithm>
+
 #include <cuda_bf16.h>
 
 #include "internal.h"
 #include "mx_common.cuh"
+#include "ptx_sm100.cuh"
 
 namespace mxb200 {
 
+__device__ uint32_t g_norm_watchdog_word;
+
 namespace {
 
-constexpr int kRows = 32;       // rows per tile
-constexpr int kThreads = 256;     // two CTAs per SM: one tile's column pass overlaps the other's row loads
-constexpr int kWarps = kThreads / 32;
-constexpr int kVec = 8;         // bf16 per 16-byte load
+constexpr int kRows = 32;  // rows per tile
+constexpr int kConsumerWarps = 16;
+constexpr int kConsumers = kConsumerWarps * 32;
+constexpr int kThreads = kConsumers + 32;  // + the producer warp
+constexpr int kVec = 8;                    // bf16 per 16-byte vector
 constexpr int kMaxCols = 2048;
+constexpr int kMaxSlots = 24;
+constexpr uint64_t kWaitLimitNs = 2000000000ull;
+constexpr uint64_t kDrainLimitNs = 50000000ull;
+
+enum Site : uint32_t { kSiteRingEmpty = 1, kSiteRingTaken = 2, kSiteRingFull = 3, kSiteRowsDone = 4, kSiteColumnsDone = 5 };
 
 struct NormParams {
   mxb200_residual_norm_mx a;
+  int slots;       // ring depth in rows
+  int inputs;      // streams per row: x (+ r) (+ x0)
   bool wide_out_t;
 };
 
-__device__ __forceinline__ float round_bf16(float v) {
-  return __bfloat162float(__float2bfloat16(v));
+// Per row of a tile: full[r] completes when the row has landed, taken[r] when its consumer has it in registers; each
+// completes once per tile and is watched by the producer and by the one warp that owns row r, phase after phase, so a
+// one-bit parity is never ambiguous. The producer re-arms full[r] only after taken[r] of the tile before, which keeps
+// it from running a whole phase ahead of a slow consumer. Per ring slot: empty[s] completes once per release.
+struct RingBarriers {
+  uint64_t full[kRows];
+  uint64_t taken[kRows];
+  uint64_t empty[kMaxSlots];
+  uint64_t tile_sync;  // the consumer warps' barrier between the row and column passes
+  uint32_t abort_flag;
+};
+
+__device__ __forceinline__ bool wait_bounded(uint64_t* bar, uint32_t parity, RingBarriers* bars, uint32_t site) {
+  if (mbar_try_wait(bar, parity))
+    return true;
+  const uint64_t t0 = global_timer_ns();
+  uint32_t spins = 0;
+  while (!mbar_try_wait(bar, parity)) {
+    if ((++spins & 63u) == 0) {
+      if (*reinterpret_cast<volatile uint32_t*>(&bars->abort_flag) != 0)
+        return false;
+      if (global_timer_ns() - t0 > kWaitLimitNs) {
+        *reinterpret_cast<volatile uint32_t*>(&bars->abort_flag) = 1;
+        atomicCAS(&g_norm_watchdog_word, 0u, 0x80000000u | (blockIdx.x << 8) | site);
+        return false;
+      }
+    }
+  }
+  return true;
 }
 
-__device__ __forceinline__ void unpack8(const uint4& raw, float (&v)[8]) {
-  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-#pragma unroll
-  for (int k = 0; k < 4; ++k) {
-    v[2 * k] = __uint_as_float(w[k] << 16);
-    v[2 * k + 1] = __uint_as_float(w[k] & 0xffff0000u);
-  }
+__device__ __forceinline__ bool wait_bounded_warp(uint64_t* bar, uint32_t parity, RingBarriers* bars, uint32_t site) {
+  return __all_sync(0xffffffffu, wait_bounded(bar, parity, bars, site)) != 0;
 }
 
-__device__ __forceinline__ uint4 pack8(const float (&v)[8]) {
-  uint4 raw;
-  uint32_t* w = reinterpret_cast<uint32_t*>(&raw);
-#pragma unroll
-  for (int k = 0; k < 4; ++k) {
-    const __nv_bfloat162 b = __floats2bfloat162_rn(v[2 * k], v[2 * k + 1]);
-    w[k] = *reinterpret_cast<const uint32_t*>(&b);
-  }
-  return raw;
+__device__ __forceinline__ uint32_t add_bf16x2(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("add.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+
+__device__ __forceinline__ uint32_t mul_bf16x2(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+
+__device__ __forceinline__ float lo_f32(uint32_t w) {
+  return __uint_as_float(w << 16);
+}
+
+__device__ __forceinline__ float hi_f32(uint32_t w) {
+  return __uint_as_float(w & 0xffff0000u);
+}
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  uint32_t d;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+  return d;
 }
 
 __device__ __forceinline__ uint32_t cvt_e4m3x4(float a, float b, float c, float d) {
@@ -65,69 +122,162 @@ __device__ __forceinline__ uint32_t cvt_e4m3x4(float a, float b, float c, float 
   return static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16);
 }
 
-__device__ __forceinline__ uint4 load16(const void* base, int64_t element) {
-  return __ldg(reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(base) + element));
+// |x| of two packed bf16 as unsigned 16-bit integers: ordered like the magnitudes, NaN above everything
+__device__ __forceinline__ uint32_t max_abs_u16x2(uint32_t m, uint32_t w) {
+  uint32_t d;
+  asm("max.u16x2 %0, %1, %2;" : "=r"(d) : "r"(m), "r"(w & 0x7fff7fffu));
+  return d;
+}
+
+// max of |x| over packed bf16 magnitudes as the quantizer takes it: fmaxf semantics, so NaN never wins
+__device__ __forceinline__ float amax_from_packed(uint32_t m, const uint32_t* words, int count) {
+  const uint32_t lo = m & 0xffffu, hi = m >> 16;
+  if (max(lo, hi) <= 0x7f80u)
+    return __uint_as_float(max(lo, hi) << 16);
+  float f = 0.f;  // a NaN among them: redo with fmaxf, which skips NaN
+  for (int k = 0; k < count; ++k)
+    f = fmaxf(f, fmaxf(fabsf(lo_f32(words[k])), fabsf(hi_f32(words[k]))));
+  return f;
 }
 
 template <int kIters>
-__global__ void __launch_bounds__(kThreads, 2) mxb200_residual_norm_mx_kernel(const NormParams p) {
-  extern __shared__ __align__(16) unsigned char smem[];
+__global__ void __launch_bounds__(kThreads, 1) mxb200_residual_norm_mx_kernel(const NormParams p) {
+  extern __shared__ __align__(128) unsigned char smem[];
   const mxb200_residual_norm_mx& a = p.a;
   const int cols = a.cols;
   const int pitch = cols + kVec;  // bf16 elements per parked row: 16 bytes of padding keep row starts on distinct banks
+  const uint32_t row_bytes = static_cast<uint32_t>(cols) * 2u;
+  const uint32_t slot_bytes = row_bytes * static_cast<uint32_t>(p.inputs);
   __nv_bfloat16* tile = reinterpret_cast<__nv_bfloat16*>(smem);
+  unsigned char* ring = smem + static_cast<size_t>(kRows) * pitch * 2;
+  RingBarriers* bars = reinterpret_cast<RingBarriers*>(ring + static_cast<size_t>(p.slots) * slot_bytes);
   const int lane = static_cast<int>(threadIdx.x) & 31, warp = static_cast<int>(threadIdx.x) >> 5;
   const bool add = a.r != nullptr, blend = a.x0 != nullptr;
-  const float lr = blend ? round_bf16(*a.lr) : 0.f, l0 = blend ? round_bf16(*a.l0) : 0.f;
+  const int slots = p.slots;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kRows; ++i) {
+      mbar_init(&bars->full[i], 1);
+      mbar_init(&bars->taken[i], 1);
+    }
+    for (int i = 0; i < slots; ++i)
+      mbar_init(&bars->empty[i], 1);
+    mbar_init(&bars->tile_sync, kConsumerWarps);
+    bars->abort_flag = 0;
+    fence_mbar_init();
+  }
+  __syncthreads();
+
+  const int64_t tiles = a.rows / kRows;
+
+  if (warp == kConsumerWarps) {
+    // ---- producer: one row per slot, in row order (the order the consumers take them)
+    const uint32_t leader = elect_one() ? 1u : 0u;
+    int slot = 0;
+    uint32_t phase = 0, tile_parity = 0;
+    int64_t issued = 0;
+    bool ok = true;
+    for (int64_t t = blockIdx.x; t < tiles && ok; t += gridDim.x, tile_parity ^= 1u) {
+      for (int r = 0; r < kRows; ++r) {
+        uint64_t* full = &bars->full[r];
+        // the slot's last row has been released, and the consumer of row r has taken the one of the tile before
+        if (!wait_bounded_warp(&bars->empty[slot], phase ^ 1u, bars, kSiteRingEmpty) ||
+            !wait_bounded_warp(&bars->taken[r], tile_parity ^ 1u, bars, kSiteRingTaken)) {
+          ok = false;
+          break;
+        }
+        const int64_t offset = (t * kRows + r) * static_cast<int64_t>(cols);
+        unsigned char* dst = ring + static_cast<size_t>(slot) * slot_bytes;
+        mbar_arrive_expect_tx(leader, full, slot_bytes);
+        bulk_load(leader, dst, static_cast<const __nv_bfloat16*>(a.x) + offset, row_bytes, full);
+        if (add)
+          bulk_load(leader, dst + row_bytes, static_cast<const __nv_bfloat16*>(a.r) + offset, row_bytes, full);
+        if (blend)
+          bulk_load(leader, dst + (add ? 2u : 1u) * row_bytes, static_cast<const __nv_bfloat16*>(a.x0) + offset,
+                    row_bytes, full);
+        ++issued;
+        if (++slot == slots) {
+          slot = 0;
+          phase ^= 1u;
+        }
+      }
+    }
+    if (!ok) {
+      // leaving early: the copies already issued must land before this CTA's shared memory is given away
+      for (int r = 0; r < kRows; ++r) {
+        const int64_t arms = (issued + kRows - 1 - r) / kRows;
+        if (arms == 0)
+          continue;
+        const uint64_t t0 = global_timer_ns();
+        while (!mbar_try_wait(&bars->full[r], static_cast<uint32_t>(arms - 1) & 1u) &&
+               global_timer_ns() - t0 < kDrainLimitNs) {
+        }
+      }
+    }
+    return;
+  }
+
+  // ---- consumers
+  const uint32_t lr2 = blend ? pack_bf16x2(*a.lr, *a.lr) : 0u, l02 = blend ? pack_bf16x2(*a.l0, *a.l0) : 0u;
   auto* out = static_cast<unsigned char*>(a.out.data);
   auto* out_scale = static_cast<unsigned char*>(a.out.scale);
   auto* out_t = static_cast<unsigned char*>(a.out_t.data);
   auto* out_t_scale = static_cast<unsigned char*>(a.out_t.scale);
+  int slot = warp % slots;  // of this warp's next row: rows advance by 16 per step, slots wrap at the ring depth
+  uint32_t sync_phase = 0, tile_parity = 0;
+  const int step = kConsumerWarps % slots;
 
-  for (int64_t row0 = static_cast<int64_t>(blockIdx.x) * kRows; row0 < a.rows; row0 += static_cast<int64_t>(gridDim.x) * kRows) {
-    // ---- rows: a warp per row, four rows per warp
-    for (int r = warp; r < kRows; r += kWarps) {
+  for (int64_t t = blockIdx.x; t < tiles; t += gridDim.x, tile_parity ^= 1u) {
+    const int64_t row0 = t * kRows;
+    for (int r = warp; r < kRows; r += kConsumerWarps) {
       const int64_t row = row0 + r;
+      if (!wait_bounded_warp(&bars->full[r], tile_parity, bars, kSiteRingFull))
+        return;
+      const uint4* sx = reinterpret_cast<const uint4*>(ring + static_cast<size_t>(slot) * slot_bytes);
+      const uint4* sr = sx + cols / kVec;
+      const uint4* sx0 = sx + (add ? 2 : 1) * (cols / kVec);
       float ss = 0.f;
       uint4 nv[kIters];
 #pragma unroll
       for (int it = 0; it < kIters; ++it) {
-        const int col = (it * 32 + lane) * kVec;
-        if (col < cols) {
-          const int64_t i = row * cols + col;
-          // loads are issued per 256-column step; the compiler hoists as many as the register budget allows and
-          // the SM's 16 warps cover the rest of the latency
-          const uint4 xs = load16(a.x, i);
-          uint4 rs = make_uint4(0, 0, 0, 0), x0s = make_uint4(0, 0, 0, 0);
-          if (add)
-            rs = load16(a.r, i);
-          if (blend)
-            x0s = load16(a.x0, i);
-          float v[8];
-          unpack8(xs, v);
+        const int vec = it * 32 + lane;
+        if (vec * kVec < cols) {
+          uint4 v = sx[vec];
+          const int64_t i = (row * cols) / kVec + vec;
           if (add) {
-            float rv[8];
-            unpack8(rs, rv);
-#pragma unroll
-            for (int k = 0; k < 8; ++k)
-              v[k] = round_bf16(v[k] + rv[k]);
+            const uint4 rv = sr[vec];
+            v = make_uint4(add_bf16x2(v.x, rv.x), add_bf16x2(v.y, rv.y), add_bf16x2(v.z, rv.z), add_bf16x2(v.w, rv.w));
             if (a.s != nullptr)
-              reinterpret_cast<uint4*>(a.s)[i / kVec] = pack8(v);
+              reinterpret_cast<uint4*>(a.s)[i] = v;
           }
+          if (!add && !blend)  // x + (-0) = x, except that a NaN leaves canonical as it does from the reference's re-rounding
+            v = make_uint4(add_bf16x2(v.x, 0x80008000u), add_bf16x2(v.y, 0x80008000u), add_bf16x2(v.z, 0x80008000u),
+                           add_bf16x2(v.w, 0x80008000u));
           if (blend) {
-            float x0v[8];
-            unpack8(x0s, x0v);
-#pragma unroll
-            for (int k = 0; k < 8; ++k)
-              v[k] = round_bf16(round_bf16(lr * v[k]) + round_bf16(l0 * x0v[k]));
+            const uint4 zv = sx0[vec];
+            v = make_uint4(add_bf16x2(mul_bf16x2(lr2, v.x), mul_bf16x2(l02, zv.x)),
+                           add_bf16x2(mul_bf16x2(lr2, v.y), mul_bf16x2(l02, zv.y)),
+                           add_bf16x2(mul_bf16x2(lr2, v.z), mul_bf16x2(l02, zv.z)),
+                           add_bf16x2(mul_bf16x2(lr2, v.w), mul_bf16x2(l02, zv.w)));
           }
+          const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-          for (int k = 0; k < 8; ++k)
-            ss = fmaf(v[k], v[k], ss);
-          nv[it] = pack8(v);
-          reinterpret_cast<uint4*>(a.res)[i / kVec] = nv[it];
+          for (int k = 0; k < 4; ++k) {
+            ss = fmaf(lo_f32(w[k]), lo_f32(w[k]), ss);
+            ss = fmaf(hi_f32(w[k]), hi_f32(w[k]), ss);
+          }
+          nv[it] = v;
+          reinterpret_cast<uint4*>(a.res)[i] = v;
         }
       }
+      __syncwarp();
+      if (lane == 0) {  // the row is in registers: the slot can take another, and row r of the next tile may be sent
+        mbar_arrive(&bars->empty[slot]);
+        mbar_arrive(&bars->taken[r]);
+      }
+      slot += step;
+      if (slot >= slots)
+        slot -= slots;
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1)
         ss += __shfl_xor_sync(0xffffffffu, ss, o);
@@ -139,29 +289,38 @@ __global__ void __launch_bounds__(kThreads, 2) mxb200_residual_norm_mx_kernel(co
       for (int it = 0; it < kIters; ++it) {
         const int col = (it * 32 + lane) * kVec;
         const bool active = col < cols;  // whole 4-lane groups: cols % 32 == 0
-        float v[8] = {};
-        float m = 0.f;
-        uint4 packed = make_uint4(0, 0, 0, 0);
+        uint32_t w[4] = {0u, 0u, 0u, 0u};
+        uint32_t m = 0u;
         if (active) {
-          unpack8(nv[it], v);
+          const uint32_t src[4] = {nv[it].x, nv[it].y, nv[it].z, nv[it].w};
 #pragma unroll
-          for (int k = 0; k < 8; ++k)
-            v[k] *= rstd;
-          packed = pack8(v);
-          unpack8(packed, v);
-          *reinterpret_cast<uint4*>(tile + r * pitch + col) = packed;
-#pragma unroll
-          for (int k = 0; k < 8; ++k)
-            m = fmaxf(m, fabsf(v[k]));
+          for (int k = 0; k < 4; ++k) {
+            w[k] = pack_bf16x2(lo_f32(src[k]) * rstd, hi_f32(src[k]) * rstd);
+            m = max_abs_u16x2(m, w[k]);
+          }
+          *reinterpret_cast<uint4*>(tile + r * pitch + col) = make_uint4(w[0], w[1], w[2], w[3]);
         }
-        m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
-        m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
+        // the block's 4 lanes agree on the packed maximum; a NaN anywhere in the warp (above 0x7f80) sends the whole
+        // warp through fmaxf, which skips NaN as the quantizer's maximum does
+        uint32_t mm = max(m & 0xffffu, m >> 16);
+        mm = max(mm, __shfl_xor_sync(0xffffffffu, mm, 1));
+        mm = max(mm, __shfl_xor_sync(0xffffffffu, mm, 2));
+        float amax = __uint_as_float(mm << 16);
+        if (__any_sync(0xffffffffu, mm > 0x7f80u)) {
+          float f = 0.f;
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            f = fmaxf(f, fmaxf(fabsf(lo_f32(w[k])), fabsf(hi_f32(w[k]))));
+          f = fmaxf(f, __shfl_xor_sync(0xffffffffu, f, 1));
+          f = fmaxf(f, __shfl_xor_sync(0xffffffffu, f, 2));
+          amax = f;
+        }
         if (active) {
-          const int e = mx_exponent(__float_as_uint(m), false);
+          const int e = mx_exponent(__float_as_uint(amax), false);
           const float mul = __uint_as_float(mx_multiplier_bits(e));
           uint2 o;
-          o.x = cvt_e4m3x4(v[0] * mul, v[1] * mul, v[2] * mul, v[3] * mul);
-          o.y = cvt_e4m3x4(v[4] * mul, v[5] * mul, v[6] * mul, v[7] * mul);
+          o.x = cvt_e4m3x4(lo_f32(w[0]) * mul, hi_f32(w[0]) * mul, lo_f32(w[1]) * mul, hi_f32(w[1]) * mul);
+          o.y = cvt_e4m3x4(lo_f32(w[2]) * mul, hi_f32(w[2]) * mul, lo_f32(w[3]) * mul, hi_f32(w[3]) * mul);
           *reinterpret_cast<uint2*>(out + row * a.out.ld + col) = o;
           if ((lane & 3) == 0) {
             const int b = col >> 5;
@@ -169,81 +328,93 @@ __global__ void __launch_bounds__(kThreads, 2) mxb200_residual_norm_mx_kernel(co
                       mx_scale_tile_offset(static_cast<int>(row & 127), b)] = static_cast<unsigned char>(e);
           }
           if (col < a.n_cols)
-            reinterpret_cast<uint4*>(a.n)[(row * cols + col) / kVec] = packed;
+            reinterpret_cast<uint4*>(a.n)[(row * cols + col) / kVec] = make_uint4(w[0], w[1], w[2], w[3]);
         }
       }
     }
-    __syncthreads();
+    __syncwarp();
+    if (lane == 0)
+      mbar_arrive(&bars->tile_sync);
+    if (!wait_bounded(&bars->tile_sync, sync_phase, bars, kSiteRowsDone))
+      return;
+    sync_phase ^= 1u;
 
-    // ---- columns: a thread owns two adjacent columns over the tile's 32 rows
-    for (int cp = static_cast<int>(threadIdx.x); cp < cols / 2; cp += kThreads) {
-      uint32_t w[kRows];
+    // ---- columns: a thread owns a column over the tile's 32 rows
+    for (int c = static_cast<int>(threadIdx.x); c < cols; c += kConsumers) {
+      uint32_t w[kRows / 2];  // rows 2k (low half) and 2k + 1 (high half)
+      uint32_t m = 0u;
 #pragma unroll
-      for (int k = 0; k < kRows; ++k)
-        w[k] = *reinterpret_cast<const uint32_t*>(tile + k * pitch + 2 * cp);
-      float mlo = 0.f, mhi = 0.f;
-#pragma unroll
-      for (int k = 0; k < kRows; ++k) {
-        mlo = fmaxf(mlo, fabsf(__uint_as_float(w[k] << 16)));
-        mhi = fmaxf(mhi, fabsf(__uint_as_float(w[k] & 0xffff0000u)));
+      for (int k = 0; k < kRows / 2; ++k) {
+        const uint32_t even = *reinterpret_cast<const unsigned short*>(tile + (2 * k) * pitch + c);
+        const uint32_t odd = *reinterpret_cast<const unsigned short*>(tile + (2 * k + 1) * pitch + c);
+        w[k] = even | (odd << 16);
+        m = max_abs_u16x2(m, w[k]);
       }
-      const int elo = mx_exponent(__float_as_uint(mlo), false), ehi = mx_exponent(__float_as_uint(mhi), false);
-      const float mullo = __uint_as_float(mx_multiplier_bits(elo)), mulhi = __uint_as_float(mx_multiplier_bits(ehi));
-      uint32_t qlo[8], qhi[8];
+      const float amax = amax_from_packed(m, w, kRows / 2);
+      const int e = mx_exponent(__float_as_uint(amax), false);
+      const float mul = __uint_as_float(mx_multiplier_bits(e));
+      uint32_t q[8];
 #pragma unroll
-      for (int k = 0; k < 8; ++k) {
-        qlo[k] = cvt_e4m3x4(__uint_as_float(w[4 * k] << 16) * mullo, __uint_as_float(w[4 * k + 1] << 16) * mullo,
-                            __uint_as_float(w[4 * k + 2] << 16) * mullo, __uint_as_float(w[4 * k + 3] << 16) * mullo);
-        qhi[k] = cvt_e4m3x4(__uint_as_float(w[4 * k] & 0xffff0000u) * mulhi,
-                            __uint_as_float(w[4 * k + 1] & 0xffff0000u) * mulhi,
-                            __uint_as_float(w[4 * k + 2] & 0xffff0000u) * mulhi,
-                            __uint_as_float(w[4 * k + 3] & 0xffff0000u) * mulhi);
-      }
-      unsigned char* dst = out_t + static_cast<int64_t>(2 * cp) * a.out_t.ld + row0;
+      for (int k = 0; k < 8; ++k)
+        q[k] = cvt_e4m3x4(lo_f32(w[2 * k]) * mul, hi_f32(w[2 * k]) * mul, lo_f32(w[2 * k + 1]) * mul,
+                          hi_f32(w[2 * k + 1]) * mul);
+      unsigned char* dst = out_t + static_cast<int64_t>(c) * a.out_t.ld + row0;
       if (p.wide_out_t) {
-        asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(dst), "r"(qlo[0]), "r"(qlo[1]), "r"(qlo[2]),
-                     "r"(qlo[3]), "r"(qlo[4]), "r"(qlo[5]), "r"(qlo[6]), "r"(qlo[7])
-                     : "memory");
-        asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(dst + a.out_t.ld), "r"(qhi[0]),
-                     "r"(qhi[1]), "r"(qhi[2]), "r"(qhi[3]), "r"(qhi[4]), "r"(qhi[5]), "r"(qhi[6]), "r"(qhi[7])
+        asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(dst), "r"(q[0]), "r"(q[1]), "r"(q[2]),
+                     "r"(q[3]), "r"(q[4]), "r"(q[5]), "r"(q[6]), "r"(q[7])
                      : "memory");
       } else {
-        reinterpret_cast<uint4*>(dst)[0] = make_uint4(qlo[0], qlo[1], qlo[2], qlo[3]);
-        reinterpret_cast<uint4*>(dst)[1] = make_uint4(qlo[4], qlo[5], qlo[6], qlo[7]);
-        reinterpret_cast<uint4*>(dst + a.out_t.ld)[0] = make_uint4(qhi[0], qhi[1], qhi[2], qhi[3]);
-        reinterpret_cast<uint4*>(dst + a.out_t.ld)[1] = make_uint4(qhi[4], qhi[5], qhi[6], qhi[7]);
+        reinterpret_cast<uint4*>(dst)[0] = make_uint4(q[0], q[1], q[2], q[3]);
+        reinterpret_cast<uint4*>(dst)[1] = make_uint4(q[4], q[5], q[6], q[7]);
       }
       const int b = static_cast<int>(row0 >> 5);
-      const int c0 = 2 * cp, c1 = 2 * cp + 1;
-      out_t_scale[(static_cast<int64_t>(c0 >> 7) * a.out_t.scale_tiles + (b >> 2)) * kScaleTileBytes +
-                  mx_scale_tile_offset(c0 & 127, b)] = static_cast<unsigned char>(elo);
-      out_t_scale[(static_cast<int64_t>(c1 >> 7) * a.out_t.scale_tiles + (b >> 2)) * kScaleTileBytes +
-                  mx_scale_tile_offset(c1 & 127, b)] = static_cast<unsigned char>(ehi);
+      out_t_scale[(static_cast<int64_t>(c >> 7) * a.out_t.scale_tiles + (b >> 2)) * kScaleTileBytes +
+                  mx_scale_tile_offset(c & 127, b)] = static_cast<unsigned char>(e);
     }
-    __syncthreads();  // before the next tile overwrites the parked rows
+    __syncwarp();
+    if (lane == 0)
+      mbar_arrive(&bars->tile_sync);  // before the next tile overwrites the parked rows
+    if (!wait_bounded(&bars->tile_sync, sync_phase, bars, kSiteColumnsDone))
+      return;
+    sync_phase ^= 1u;
   }
 }
 
 template <int kIters>
-int launch(const NormParams& p, int sms, cudaStream_t stream) {
-  const size_t smem = static_cast<size_t>(kRows) * (kIters * 256 + kVec) * sizeof(__nv_bfloat16);
+int launch(NormParams& p, const DeviceInfo& dev, cudaStream_t stream) {
+  const size_t tile_bytes = static_cast<size_t>(kRows) * (p.a.cols + kVec) * sizeof(__nv_bfloat16);
+  const size_t slot_bytes = static_cast<size_t>(p.inputs) * p.a.cols * sizeof(__nv_bfloat16);
+  const size_t fixed = tile_bytes + sizeof(RingBarriers) + 128;
+  if (static_cast<size_t>(dev.smem_optin) < fixed + 2 * slot_bytes)
+    return MXB200_ERR_SHAPE;
+  p.slots = static_cast<int>(std::min<size_t>(kMaxSlots, (dev.smem_optin - fixed) / slot_bytes));
+  const size_t smem = tile_bytes + p.slots * slot_bytes + sizeof(RingBarriers);
   static std::atomic<int> configured_for{-1};
-  int device = 0;
-  cudaGetDevice(&device);
-  if (smem > 48 * 1024 && configured_for.load() != device) {
+  if (configured_for.load() != dev.device) {
     if (cudaFuncSetAttribute(mxb200_residual_norm_mx_kernel<kIters>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             static_cast<int>(smem)) != cudaSuccess)
+                             dev.smem_optin) != cudaSuccess)
       return MXB200_ERR_LAUNCH;
-    configured_for.store(device);
+    configured_for.store(dev.device);
   }
   const int64_t tiles = p.a.rows / kRows;
-  const int grid = static_cast<int>(std::min<int64_t>(tiles, 2 * static_cast<int64_t>(sms)));
+  const int grid = static_cast<int>(std::min<int64_t>(tiles, static_cast<int64_t>(dev.sms)));
   mxb200_residual_norm_mx_kernel<kIters><<<grid, kThreads, smem, stream>>>(p);
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return launch_status();
 }
 
 }  // namespace
+
+uint32_t take_norm_watchdog_word() {
+  uint32_t w = 0;
+  if (cudaMemcpyFromSymbol(&w, g_norm_watchdog_word, sizeof(w)) != cudaSuccess)
+    return 0;
+  if (w != 0) {
+    const uint32_t zero = 0;
+    cudaMemcpyToSymbol(g_norm_watchdog_word, &zero, sizeof(zero));
+  }
+  return w;
+}
 
 }  // namespace mxb200
 
@@ -260,8 +431,8 @@ extern "C" int mxb200_residual_norm_mx_fwd(const mxb200_residual_norm_mx* args, 
       (a.n_cols > 0 && a.n == nullptr))
     return MXB200_ERR_NULL;
   if (a.rows <= 0 || a.cols <= 0 || a.rows % 128 != 0 || a.cols % 128 != 0 || a.cols > kMaxCols || a.n_cols < 0 ||
-      a.n_cols > a.cols || a.out.ld < a.cols || a.out_t.ld < a.rows ||
-      a.out.scale_tiles < a.cols / 128 || a.out_t.scale_tiles < a.rows / 128)
+      a.n_cols > a.cols || a.out.ld < a.cols || a.out_t.ld < a.rows || a.out.scale_tiles < a.cols / 128 ||
+      a.out_t.scale_tiles < a.rows / 128)
     return MXB200_ERR_SHAPE;
   for (const void* ptr : {a.x, a.r, a.x0, static_cast<const void*>(a.s), static_cast<const void*>(a.res),
                           static_cast<const void*>(a.n), static_cast<const void*>(a.out.data),
@@ -271,16 +442,17 @@ extern "C" int mxb200_residual_norm_mx_fwd(const mxb200_residual_norm_mx* args, 
       return MXB200_ERR_ALIGNMENT;
   if (a.out.ld % 16 != 0 || a.out_t.ld % 16 != 0)
     return MXB200_ERR_ALIGNMENT;
-  NormParams p{a, (reinterpret_cast<uintptr_t>(a.out_t.data) & 31u) == 0 && a.out_t.ld % 32 == 0};
+  NormParams p{a, 0, 1 + (a.r != nullptr) + (a.x0 != nullptr),
+               (reinterpret_cast<uintptr_t>(a.out_t.data) & 31u) == 0 && a.out_t.ld % 32 == 0};
   auto* s = static_cast<cudaStream_t>(stream);
   switch ((a.cols + 255) / 256) {
-    case 1: return launch<1>(p, dev.sms, s);
-    case 2: return launch<2>(p, dev.sms, s);
-    case 3: return launch<3>(p, dev.sms, s);
-    case 4: return launch<4>(p, dev.sms, s);
-    case 5: return launch<5>(p, dev.sms, s);
-    case 6: return launch<6>(p, dev.sms, s);
-    case 7: return launch<7>(p, dev.sms, s);
-    default: return launch<8>(p, dev.sms, s);
+    case 1: return launch<1>(p, dev, s);
+    case 2: return launch<2>(p, dev, s);
+    case 3: return launch<3>(p, dev, s);
+    case 4: return launch<4>(p, dev, s);
+    case 5: return launch<5>(p, dev, s);
+    case 6: return launch<6>(p, dev, s);
+    case 7: return launch<7>(p, dev, s);
+    default: return launch<8>(p, dev, s);
   }
 }

@@ -69,6 +69,50 @@ def test_matches_oracle(rows, cols, add, blend):
     assert_quantized_equal(n_mx, mo.quantize_mx(o_n), what)
 
 
+@pytest.mark.parametrize("add,blend", COMBOS)
+def test_special_values_match_reference_kernel(add, blend):
+    """NaN, infinities, bf16 subnormals, values whose squares overflow, an all-zero row: the packed bf16 add and
+    blend and the packed maximum must still give the reference kernel's bits."""
+    if not refkernel.available():
+        pytest.skip("reference kernel library not built")
+    rows, cols = 128, 512
+    inp = residual_norm_inputs(rows, cols, add, blend, seed=9)
+    x = inp["x"].float()
+    x[5, 17] = float("nan")
+    x[6, 300] = float("inf")
+    x[7, 40] = float("-inf")
+    x[8, :] = 0
+    x[9, 0:64] = 1e-39
+    x[9, 64:128] = -3e-40
+    x[10, :] = x[10, :] * 1e-38
+    x[11, 100:132] = 3e38
+    x[12, :] = x[12, :] * 1e19
+    x[13, 33] = -0.0
+    inp["x"] = x.to(torch.bfloat16)
+    if add:
+        r = inp["r"].float()
+        r[9, 0:64] = -1e-39          # exact cancellation of subnormals
+        r[10, :] = r[10, :] * 1e-38
+        r[8, :] = 0
+        r[14, 7] = float("nan")
+        inp["r"] = r.to(torch.bfloat16)
+    if blend:
+        x0 = inp["x0"].float()
+        x0[8, :] = 0
+        x0[10, :] = x0[10, :] * 1e-37
+        x0[15, 9] = float("inf")
+        inp["x0"] = x0.to(torch.bfloat16)
+    res, n, n_mx, rstd, s = run(inp, cols)
+    c = lambda t: None if t is None else t.cuda()
+    ref = refkernel.residual_norm(c(inp["x"]), c(inp["r"]), c(inp["x0"]), c(inp["lr"]), c(inp["l0"]), inp["layer"], cols)
+    assert np.array_equal(bits(res), bits(ref["res"]))
+    assert np.array_equal(np_f32(rstd).view(np.uint32), np_f32(ref["rstd"]).view(np.uint32))
+    if s is not None:
+        assert np.array_equal(bits(s), bits(ref["s"]))
+    assert np.array_equal(bits(n), bits(ref["n"]))
+    assert_quantized_equal(n_mx, {k: np_u8(ref[k]) for k in ("data", "scale", "data_t", "scale_t")}, "special values")
+
+
 def test_mx_is_quantize_of_n_at_full_size():
     """The reference's property (tests/test_residual_norm.cpp:179-186) on the d24 activation: the MX output is
     quantize_mx of the bf16 n, both layouts."""
