@@ -122,6 +122,14 @@ __device__ __forceinline__ uint32_t cvt_e4m3x4(float a, float b, float c, float 
   return static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16);
 }
 
+// e4m3 of four bf16 values (two packed words) times a power of two given as packed bf16. The multiplier is a power
+// of two, so the packed bf16 product equals the fp32 product wherever the result is a normal bf16; below that
+// (|v| < 2^-126) both forms round to zero in e4m3.
+__device__ __forceinline__ uint32_t cvt_e4m3x4_scaled(uint32_t w0, uint32_t w1, uint32_t mul2) {
+  const uint32_t a = mul_bf16x2(w0, mul2), b = mul_bf16x2(w1, mul2);
+  return cvt_e4m3x4(lo_f32(a), hi_f32(a), lo_f32(b), hi_f32(b));
+}
+
 // |x| of two packed bf16 as unsigned 16-bit integers: ordered like the magnitudes, NaN above everything
 __device__ __forceinline__ uint32_t max_abs_u16x2(uint32_t m, uint32_t w) {
   uint32_t d;
@@ -233,28 +241,29 @@ __global__ void __launch_bounds__(kThreads, 1) mxb200_residual_norm_mx_kernel(co
       const int64_t row = row0 + r;
       if (!wait_bounded_warp(&bars->full[r], tile_parity, bars, kSiteRingFull))
         return;
-      const uint4* sx = reinterpret_cast<const uint4*>(ring + static_cast<size_t>(slot) * slot_bytes);
+      // lane-based pointers: every access of the row below is one of these plus a compile-time multiple of 512 bytes
+      const uint4* sx = reinterpret_cast<const uint4*>(ring + static_cast<size_t>(slot) * slot_bytes) + lane;
       const uint4* sr = sx + cols / kVec;
       const uint4* sx0 = sx + (add ? 2 : 1) * (cols / kVec);
+      uint4* res_row = reinterpret_cast<uint4*>(a.res) + (row * cols) / kVec + lane;
+      uint4* s_row = (add && a.s != nullptr) ? reinterpret_cast<uint4*>(a.s) + (row * cols) / kVec + lane : nullptr;
       float ss = 0.f;
       uint4 nv[kIters];
 #pragma unroll
       for (int it = 0; it < kIters; ++it) {
-        const int vec = it * 32 + lane;
-        if (vec * kVec < cols) {
-          uint4 v = sx[vec];
-          const int64_t i = (row * cols) / kVec + vec;
+        if ((it * 32 + lane) * kVec < cols) {
+          uint4 v = sx[it * 32];
           if (add) {
-            const uint4 rv = sr[vec];
+            const uint4 rv = sr[it * 32];
             v = make_uint4(add_bf16x2(v.x, rv.x), add_bf16x2(v.y, rv.y), add_bf16x2(v.z, rv.z), add_bf16x2(v.w, rv.w));
-            if (a.s != nullptr)
-              reinterpret_cast<uint4*>(a.s)[i] = v;
+            if (s_row != nullptr)
+              s_row[it * 32] = v;
           }
           if (!add && !blend)  // x + (-0) = x, except that a NaN leaves canonical as it does from the reference's re-rounding
             v = make_uint4(add_bf16x2(v.x, 0x80008000u), add_bf16x2(v.y, 0x80008000u), add_bf16x2(v.z, 0x80008000u),
                            add_bf16x2(v.w, 0x80008000u));
           if (blend) {
-            const uint4 zv = sx0[vec];
+            const uint4 zv = sx0[it * 32];
             v = make_uint4(add_bf16x2(mul_bf16x2(lr2, v.x), mul_bf16x2(l02, zv.x)),
                            add_bf16x2(mul_bf16x2(lr2, v.y), mul_bf16x2(l02, zv.y)),
                            add_bf16x2(mul_bf16x2(lr2, v.z), mul_bf16x2(l02, zv.z)),
@@ -267,7 +276,7 @@ __global__ void __launch_bounds__(kThreads, 1) mxb200_residual_norm_mx_kernel(co
             ss = fmaf(hi_f32(w[k]), hi_f32(w[k]), ss);
           }
           nv[it] = v;
-          reinterpret_cast<uint4*>(a.res)[i] = v;
+          res_row[it * 32] = v;
         }
       }
       __syncwarp();
@@ -285,6 +294,12 @@ __global__ void __launch_bounds__(kThreads, 1) mxb200_residual_norm_mx_kernel(co
       if (lane == 0)
         a.rstd[row] = rstd;
       // n = bf16(res * rstd): parked for the column pass, quantized row-wise from registers (4 lanes per block)
+      uint4* tile_row = reinterpret_cast<uint4*>(tile + r * pitch) + lane;
+      uint2* out_row = reinterpret_cast<uint2*>(out + row * a.out.ld) + lane;
+      uint4* n_row = reinterpret_cast<uint4*>(a.n) + (row * cols) / kVec + lane;
+      // the scale byte of block b = it * 8 + lane / 4 sits at tile (row / 128, b / 4), byte offset(row % 128, b % 4)
+      unsigned char* scale_row = out_scale + (static_cast<int64_t>(row >> 7) * a.out.scale_tiles + (lane >> 4)) * kScaleTileBytes +
+                                 mx_scale_tile_offset(static_cast<int>(row & 127), (lane >> 2) & 3);
 #pragma unroll
       for (int it = 0; it < kIters; ++it) {
         const int col = (it * 32 + lane) * kVec;
@@ -298,7 +313,7 @@ __global__ void __launch_bounds__(kThreads, 1) mxb200_residual_norm_mx_kernel(co
             w[k] = pack_bf16x2(lo_f32(src[k]) * rstd, hi_f32(src[k]) * rstd);
             m = max_abs_u16x2(m, w[k]);
           }
-          *reinterpret_cast<uint4*>(tile + r * pitch + col) = make_uint4(w[0], w[1], w[2], w[3]);
+          tile_row[it * 32] = make_uint4(w[0], w[1], w[2], w[3]);
         }
         // the block's 4 lanes agree on the packed maximum; a NaN anywhere in the warp (above 0x7f80) sends the whole
         // warp through fmaxf, which skips NaN as the quantizer's maximum does
@@ -317,18 +332,15 @@ __global__ void __launch_bounds__(kThreads, 1) mxb200_residual_norm_mx_kernel(co
         }
         if (active) {
           const int e = mx_exponent(__float_as_uint(amax), false);
-          const float mul = __uint_as_float(mx_multiplier_bits(e));
+          const uint32_t mul2 = (mx_multiplier_bits(e) >> 16) * 0x10001u;
           uint2 o;
-          o.x = cvt_e4m3x4(lo_f32(w[0]) * mul, hi_f32(w[0]) * mul, lo_f32(w[1]) * mul, hi_f32(w[1]) * mul);
-          o.y = cvt_e4m3x4(lo_f32(w[2]) * mul, hi_f32(w[2]) * mul, lo_f32(w[3]) * mul, hi_f32(w[3]) * mul);
-          *reinterpret_cast<uint2*>(out + row * a.out.ld + col) = o;
-          if ((lane & 3) == 0) {
-            const int b = col >> 5;
-            out_scale[(static_cast<int64_t>(row >> 7) * a.out.scale_tiles + (b >> 2)) * kScaleTileBytes +
-                      mx_scale_tile_offset(static_cast<int>(row & 127), b)] = static_cast<unsigned char>(e);
-          }
+          o.x = cvt_e4m3x4_scaled(w[0], w[1], mul2);
+          o.y = cvt_e4m3x4_scaled(w[2], w[3], mul2);
+          out_row[it * 32] = o;
+          if ((lane & 3) == 0)
+            scale_row[it * 2 * kScaleTileBytes] = static_cast<unsigned char>(e);
           if (col < a.n_cols)
-            reinterpret_cast<uint4*>(a.n)[(row * cols + col) / kVec] = make_uint4(w[0], w[1], w[2], w[3]);
+            n_row[it * 32] = make_uint4(w[0], w[1], w[2], w[3]);
         }
       }
     }
@@ -352,12 +364,11 @@ __global__ void __launch_bounds__(kThreads, 1) mxb200_residual_norm_mx_kernel(co
       }
       const float amax = amax_from_packed(m, w, kRows / 2);
       const int e = mx_exponent(__float_as_uint(amax), false);
-      const float mul = __uint_as_float(mx_multiplier_bits(e));
+      const uint32_t mul2 = (mx_multiplier_bits(e) >> 16) * 0x10001u;
       uint32_t q[8];
 #pragma unroll
       for (int k = 0; k < 8; ++k)
-        q[k] = cvt_e4m3x4(lo_f32(w[2 * k]) * mul, hi_f32(w[2 * k]) * mul, lo_f32(w[2 * k + 1]) * mul,
-                          hi_f32(w[2 * k + 1]) * mul);
+        q[k] = cvt_e4m3x4_scaled(w[2 * k], w[2 * k + 1], mul2);
       unsigned char* dst = out_t + static_cast<int64_t>(c) * a.out_t.ld + row0;
       if (p.wide_out_t) {
         asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(dst), "r"(q[0]), "r"(q[1]), "r"(q[2]),
