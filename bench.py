@@ -32,6 +32,10 @@ sys.path.insert(0, ROOT)
 METRIC = "MXFP8 linear TFLOP/s/GPU, d24 fwd+dgrad+wgrad shapes, % of FP8 tensor peak"
 WORKLOAD = "d24 data-parallel step GEMM set: 24 x (QKV, attn-out, MLP fc, MLP proj) + lm_head in 2048-row chunks, fwd+dgrad+wgrad, M=16384 tokens/rank"
 FP8_SPEC_TFLOPS = 4500.0  # B200 dense FP8, 2x the 2.25e15 bf16 figure
+# dram__bytes_read.sum + dram__bytes_write.sum of one captured launch of the GEMM kernel, the merged-QKV forward
+# (M=16384, N=4608, K=1536, bf16 out): profiles/gemm_pair_kernel_d24_shapes.md. Its algorithmic bytes: 184.3e6.
+GEMM_TRAFFIC_BYTES = 171.8e6
+GEMM_TRAFFIC_LAUNCH = "qkv.fwd 16384x4608x1536 (algorithmic 184.3 MB; the step's other launches differ in shape)"
 
 
 def measured_peaks():
@@ -263,7 +267,8 @@ def run_gpu_arm(args):
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             "gpu_launches": int(launches),
             "roofline": {"bound": "tensor", "kernel": "mxb200_mx_gemm_pair_kernel (256x192 and 256x256 tiles)", "achieved": achieved, "peak": fp8_peak,
-                         "unit": "TFLOP/s", "frac": achieved / fp8_peak, "traffic": None,
+                         "unit": "TFLOP/s", "frac": achieved / fp8_peak, "traffic": GEMM_TRAFFIC_BYTES,
+                         "traffic_launch": GEMM_TRAFFIC_LAUNCH,
                          "peak_source": f"2 x bf16_tflops_sustained of {peaks['source']} (no FP8 GEMM peak was measured; the FP8 pipe runs at twice the bf16 rate)",
                          "launches": n_gemm, "avg_launch_us": gemm_ms * 1e3 / max(n_gemm, 1)},
             "quantizer": {"bound": "hbm", "kernel": "mxb200_quantize_kernel", "achieved": cfg.quantized_bytes_per_step() * args.steps / (quant_ms * 1e-3) / 1e9,
