@@ -1,8 +1,8 @@
 // C++ face of libmxb200 at nanochat-cpp's kernel seam.
 //
 // nanochat-cpp keeps its CUDA kernels behind free functions in namespace nanochat::kernels whose headers include
-// only <cstdint> and <cuda_runtime_api.h> (src/nanochat/model/fp8/fp8_kernel.h:1-10, mx_gemm_kernel.h:5-9). This
-// header offers the MX subset of that seam with the SAME names, parameter lists and conventions, implemented as
+// only <cstdint> and <cuda_runtime_api.h> (src/nanochat/model/fp8/fp8_kernel.h:1-10, mx_gemm_kernel.h:5-9,
+// ops/residual_norm_kernel.h:1-10). This header offers the MX subset of that seam with the SAME names, parameter lists and conventions, implemented as
 // inline calls into the C ABI of include/mxb200.h: a translation unit of the reference that includes this header
 // instead of fp8_kernel.h / mx_gemm_kernel.h, and links libmxb200.so, runs its MX path on the B200 engine.
 //   - quantizer launchers return void and leave errors to cudaGetLastError-style checks in the reference
@@ -93,6 +93,54 @@ inline const char* b200_mx_gemm_f32_splitk(const void* a, const void* a_scale, c
     splits = mxb200_gemm_splits(M, N, K);
   return b200_detail::message(mxb200_gemm_splitk(a, a_scale, b, b_scale, d, MXB200_OUT_F32, nullptr, M, N, K, alpha,
                                                  accumulate ? 1 : 0, splits, workspace, workspace_bytes, stream));
+}
+
+// Same contract as cutlass_mx_gemm_relu_square (src/nanochat/model/fp8/mx_gemm_kernel.h:24-27): h = a . b^T in bf16 and,
+// from the same epilogue, quantize_mx(h, relu_square = true) into q (M, N) and q_t (N, M), bit for bit.
+inline const char* b200_mx_gemm_relu_square(const void* a, const void* a_scale, const void* b, const void* b_scale,
+                                            void* h, void* q, void* q_scale, void* q_t, void* q_t_scale, int64_t M,
+                                            int64_t N, int64_t K, cudaStream_t stream) {
+  return b200_detail::message(
+        mxb200_gemm_relu_square(a, a_scale, b, b_scale, h, q, q_scale, q_t, q_t_scale, M, N, K, stream));
+}
+
+// Same contract as cutlass_mx_gemm_relu_square_bwd (src/nanochat/model/fp8/mx_gemm_kernel.h:29-32): ga = a . b^T is not
+// written; with h (M, N) bf16 the epilogue gives quantize_mx_relu_square_bwd(ga, h) into dh (M, N) and dh_t (N, M).
+inline const char* b200_mx_gemm_relu_square_bwd(const void* a, const void* a_scale, const void* b, const void* b_scale,
+                                                const void* h, void* dh, void* dh_scale, void* dh_t, void* dh_t_scale,
+                                                int64_t M, int64_t N, int64_t K, cudaStream_t stream) {
+  return b200_detail::message(
+        mxb200_gemm_relu_square_bwd(a, a_scale, b, b_scale, h, dh, dh_scale, dh_t, dh_t_scale, M, N, K, stream));
+}
+
+// src/nanochat/model/ops/residual_norm_kernel.h:17-31 and :33-41, field for field.
+struct ResidualNormFwd {
+  const void *x, *r, *x0;
+  const float *lr, *l0;
+  void* s;
+  void *res, *n;
+  float* rstd;
+  int64_t rows;
+  int cols;
+  float eps;
+};
+
+struct ResidualNormMxFwd {
+  ResidualNormFwd base;
+  MxOut out, out_t;
+  int n_cols;
+};
+
+// This library's limit on cols (the reference's kResidualNormMxMaxCols is 1536, residual_norm_kernel.h:15).
+inline constexpr int kResidualNormMxMaxCols = 2048;
+
+// src/nanochat/model/ops/residual_norm_kernel.h:44; a failing status is kept for last_status(), as for the quantizer.
+inline void residual_norm_mx_fwd(const ResidualNormMxFwd& a, cudaStream_t stream) {
+  const mxb200_residual_norm_mx args{a.base.x,    a.base.r,    a.base.x0,  a.base.lr,
+                                     a.base.l0,   a.base.s,    a.base.res, a.base.n,
+                                     a.base.rstd, a.base.rows, a.base.cols, a.base.eps,
+                                     b200_detail::view(a.out), b200_detail::view(a.out_t), a.n_cols};
+  b200_detail::status_slot() = mxb200_residual_norm_mx_fwd(&args, stream);
 }
 
 }  // namespace nanochat::kernels

@@ -20,7 +20,14 @@ int main() {
   void (*qb)(const void*, const void*, int64_t, int64_t, k::MxOut, k::MxOut, cudaStream_t) = &k::quantize_mx_relu_square_bwd;
   const char* (*g16)(const void*, const void*, const void*, const void*, void*, int64_t, int64_t, int64_t, cudaStream_t) = &k::b200_mx_gemm_bf16;
   const char* (*g32)(const void*, const void*, const void*, const void*, float*, int64_t, int64_t, int64_t, const float*, bool, cudaStream_t) = &k::b200_mx_gemm_f32;
-  (void)q; (void)qb; (void)g16; (void)g32;
+  const char* (*gr)(const void*, const void*, const void*, const void*, void*, void*, void*, void*, void*, int64_t, int64_t, int64_t, cudaStream_t) = &k::b200_mx_gemm_relu_square;
+  const char* (*grb)(const void*, const void*, const void*, const void*, const void*, void*, void*, void*, void*, int64_t, int64_t, int64_t, cudaStream_t) = &k::b200_mx_gemm_relu_square_bwd;
+  void (*rn)(const k::ResidualNormMxFwd&, cudaStream_t) = &k::residual_norm_mx_fwd;
+  (void)q; (void)qb; (void)g16; (void)g32; (void)gr; (void)grb; (void)rn;
+  k::ResidualNormMxFwd norm{};
+  norm.base.rows = 128, norm.base.cols = 128;
+  k::residual_norm_mx_fwd(norm, nullptr);
+  if (k::last_status() == MXB200_OK) return 2;
   // without an sm_100 device every call refuses with a message instead of computing on the host
   const char* msg = k::b200_mx_gemm_bf16(nullptr, nullptr, nullptr, nullptr, nullptr, 128, 128, 128, nullptr);
   k::MxOut none{nullptr, 0, nullptr, 0};
