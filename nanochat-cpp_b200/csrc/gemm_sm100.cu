@@ -27,6 +27,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
+#include "bf16x2_sm100.cuh"
 #include "internal.h"
 #include "mx_common.cuh"
 #include "ptx_sm100.cuh"
@@ -46,7 +47,13 @@ static __device__ __align__(256) unsigned char g_static_splitk_scratch[MXB200_ST
 __device__ unsigned long long g_trace[8192];
 #define TRACE(slot, idx) \
   do { if (blockIdx.x == 0 && (idx) < 64) g_trace[(slot) * 64 + (idx)] = clock64(); } while (0)
+__device__ int g_exp;  // experiment switch of the tracing build
+__device__ int g_chunk_calls;
+#define STAMP(k) do { if (stamp) g_trace[5 * 64 + (k)] = clock64(); } while (0)
+#define EXP(bit) ((g_exp >> (bit)) & 1)
 #else
+#define EXP(bit) 0
+#define STAMP(k) do { } while (0)
 #define TRACE(slot, idx) do { } while (0)
 #endif
 
@@ -631,19 +638,11 @@ __global__ void __launch_bounds__(kThreads, 1)
 //   rows:    a thread holds its row's 32 columns = one scale block: no communication.
 //   columns: the block goes through shared memory (bf16, the 64-byte-swizzled 2 KB tile the output store uses),
 //            lane j then reads column j's 32 rows = one scale block of the transposed layout.
-// Both results are parked as 32 rows x 32 bytes and leave by TMA store; scale bytes go straight to their swizzled
-// positions. Layout of `stage` (6 KB per warp): [0,2K) output rows, [2K,4K) transpose tile, [4K,5K) q, [5K,6K) q_t.
-
-__device__ __forceinline__ uint32_t e4m3x4(float a, float b, float c, float d) {
-  uint16_t lo, hi;
-  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %2, %1;" : "=h"(lo) : "f"(a), "f"(b));
-  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %2, %1;" : "=h"(hi) : "f"(c), "f"(d));
-  return static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16);
-}
-
-__device__ __forceinline__ float bf16_round(float v) {
-  return __bfloat162float(__float2bfloat16(v));
-}
+// Both results are parked as 32 rows x 32 bytes (16-byte halves placed by the 32-byte swizzle their tensor maps
+// expect, which keeps the 16-byte stores of a quarter warp on distinct banks) and leave by TMA store; scale bytes go
+// straight to their swizzled positions. The values stay packed bf16x2 throughout (bf16x2_sm100.cuh says why that
+// gives the bits of the fp32-then-round form). Layout of `stage` (6 KB per warp): [0,2K) output rows, [2K,4K)
+// transpose tile, [4K,5K) q, [5K,6K) q_t.
 
 // The relu^2 backward form's second input: this lane's four 16-byte pieces of the 32 x 32 bf16 block of h at
 // (warp_row0, col). Zeros outside the matrix.
@@ -658,35 +657,57 @@ __device__ __forceinline__ void load_h_pieces(const GemmParams& p, int lane, int
   }
 }
 
+// Quantizes one scale block held as 16 packed words (32 bf16 in block order) into 32 e4m3 bytes w[8]; returns the
+// block's biased exponent.
+__device__ __forceinline__ int quantize_block(const uint32_t* v, int floor_rule, uint32_t* w) {
+  uint32_t m = 0u;
+#pragma unroll
+  for (int k = 0; k < 16; ++k)
+    m = max_abs_u16x2(m, v[k]);
+  const int e = mx_exponent(__float_as_uint(amax_from_packed(m, v, 16)), floor_rule);
+  const uint32_t mul2 = (mx_multiplier_bits(e) >> 16) * 0x10001u;
+#pragma unroll
+  for (int k = 0; k < 8; ++k)
+    w[k] = e4m3x4_scaled(v[2 * k], v[2 * k + 1], mul2);
+  return e;
+}
+
+// Parks a block's 32 bytes as row `lane` of a 32 x 32-byte staging tile in the 32-byte swizzle (the 16-byte half
+// index is xor-ed with bit 7 of the offset).
+__device__ __forceinline__ void park_block(const uint32_t* w, unsigned char* st, int lane) {
+  const int flip = ((lane >> 2) & 1) << 4;
+  *reinterpret_cast<uint4*>(st + lane * 32 + flip) = make_uint4(w[0], w[1], w[2], w[3]);
+  *reinterpret_cast<uint4*>(st + lane * 32 + (flip ^ 16)) = make_uint4(w[4], w[5], w[6], w[7]);
+}
+
 template <int kFuse>
 __device__ __forceinline__ void fused_quantize_chunk(const GemmParams& p, const CUtensorMap* map_d,
                                                      const CUtensorMap* map_q, const CUtensorMap* map_qt,
                                                      unsigned char* stage, int lane, const float* acc, int64_t row,
                                                      int col, int warp_row0, bool valid, const uint4* h_pieces) {
-  unsigned char* st_out = stage;
-  unsigned char* st_tr = stage + 2048;
-  unsigned char* st_q = stage + 4096;
-  unsigned char* st_qt = stage + 5120;
-  if (lane == 0)
-    tma_store_wait_read<0>();  // the previous chunk's stores have been read out of all four buffers
-  __syncwarp();
+  unsigned char* st_out = stage;         // TMA source (forward form); h hand-over buffer (backward form, never a source)
+  unsigned char* st_tr = stage + 2048;   // transpose tile, only ever touched by this warp's threads
+  unsigned char* st_q = stage + 4096;    // TMA source
+  unsigned char* st_qt = stage + 5120;   // TMA source
+  // The previous chunk's TMA stores may still be reading st_out / st_q / st_qt: everything up to the point where those
+  // are written again (all of the arithmetic) runs first, and only then does the warp wait for the reads to finish.
 
-  // ---- the values to quantize, v[32], bf16-exact
-  float v[32];
+#ifdef MXB200_TRACE
+  bool stamp = false;
+  if (blockIdx.x == 0 && threadIdx.x == 64)
+    stamp = (g_chunk_calls++ == 21);
+#endif
+  STAMP(0);
+  // ---- the values to quantize: this thread's row of the block, 32 bf16 as 16 packed words
+  uint32_t v[16];
+  uint32_t o[kFuse == kFuseReluSquare ? 16 : 1];
   if constexpr (kFuse == kFuseReluSquare) {
-    uint32_t o[16];
 #pragma unroll
     for (int k = 0; k < 16; ++k) {
-      o[k] = pack_bf16x2(acc[2 * k], acc[2 * k + 1]);
-      const float h0 = __uint_as_float(o[k] << 16), h1 = __uint_as_float(o[k] & 0xffff0000u);
-      const float r0 = h0 <= 0.f ? 0.f : h0, r1 = h1 <= 0.f ? 0.f : h1;
-      v[2 * k] = bf16_round(r0 * r0);
-      v[2 * k + 1] = bf16_round(r1 * r1);
+      o[k] = pack_bf16x2_rn(acc[2 * k], acc[2 * k + 1]);
+      const uint32_t r = relu_keep_nan_bf16x2(o[k]);
+      v[k] = mul_bf16x2(r, r);
     }
-#pragma unroll
-    for (int j = 0; j < 4; ++j)  // h itself leaves as the plain epilogue's output does
-      *reinterpret_cast<uint4*>(st_out + lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4)) =
-            make_uint4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
   } else {
     // h's 32 x 32 block was loaded coalesced (load_h_pieces: 4 lanes per 64-byte row segment, 8 rows per
     // instruction, issued a chunk ahead) and is handed to the row owners through the otherwise unused output buffer
@@ -703,87 +724,103 @@ __device__ __forceinline__ void fused_quantize_chunk(const GemmParams& p, const 
         const uint4 t = *reinterpret_cast<const uint4*>(st_out + lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4));
         hw[4 * j] = t.x, hw[4 * j + 1] = t.y, hw[4 * j + 2] = t.z, hw[4 * j + 3] = t.w;
       }
+      __syncwarp();  // all rows read before the next chunk's pieces overwrite them
     } else {
 #pragma unroll
       for (int k = 0; k < 16; ++k)
         hw[k] = 0;
     }
 #pragma unroll
-    for (int k = 0; k < 16; ++k) {
-      const float g0 = bf16_round(acc[2 * k]), g1 = bf16_round(acc[2 * k + 1]);
-      const float h0 = __uint_as_float(hw[k] << 16), h1 = __uint_as_float(hw[k] & 0xffff0000u);
-      v[2 * k] = bf16_round(h0 <= 0.f ? 0.f : g0 * (2.f * h0));
-      v[2 * k + 1] = bf16_round(h1 <= 0.f ? 0.f : g1 * (2.f * h1));
+    for (int k = 0; k < 16; ++k) {  // dh = bf16(h <= 0 ? 0 : bf16(ga) * 2h)
+      const uint32_t g = pack_bf16x2_rn(acc[2 * k], acc[2 * k + 1]);
+      v[k] = mul_bf16x2(g, add_bf16x2(hw[k], hw[k])) & positive_or_nan_mask_bf16x2(hw[k]);
     }
   }
+
+  STAMP(1);
+  // ---- columns, first half: into the transpose tile, 64 bytes per column (its 32 rows as bf16). A store instruction
+  // puts one column's 32 rows there (32 lanes x 2 bytes, conflict-free); the 16-byte pieces of column c sit at piece
+  // index xor (c >> 1) & 3, so that lane c then reads its column as four 16-byte vectors without bank conflicts.
+  {
+    unsigned char* mine[4];
+#pragma unroll
+    for (int x = 0; x < 4; ++x)
+      mine[x] = st_tr + ((((lane >> 3) ^ x) << 4) | ((lane & 7) << 1));
+#pragma unroll
+    for (int k = 0; k < 16; ++k) {
+      *reinterpret_cast<uint16_t*>(mine[k & 3] + (2 * k) * 64) = static_cast<uint16_t>(v[k]);
+      *reinterpret_cast<uint16_t*>(mine[k & 3] + (2 * k + 1) * 64) = static_cast<uint16_t>(v[k] >> 16);
+    }
+  }
+  STAMP(2);
+  __syncwarp();
+  STAMP(3);
 
   // ---- rows: this thread's 32 values are one block
+  uint32_t wq[8];
+  int e_row = 0;
+  if (!EXP(1))
+    e_row = quantize_block(v, p.floor_rule, wq);
+  else
+    for (int k = 0; k < 8; ++k) wq[k] = v[k];
+
+  STAMP(4);
+  // ---- columns, second half: lane c owns column c
+  uint32_t wqt[8];
+  int e_col;
   {
-    float m = 0.f;
+    uint32_t c[16];
 #pragma unroll
-    for (int k = 0; k < 32; ++k)
-      m = fmaxf(m, fabsf(v[k]));
-    const int e = mx_exponent(__float_as_uint(m), p.floor_rule);
-    const float mul = __uint_as_float(mx_multiplier_bits(e));
-    uint32_t w[8];
-#pragma unroll
-    for (int k = 0; k < 8; ++k)
-      w[k] = e4m3x4(v[4 * k] * mul, v[4 * k + 1] * mul, v[4 * k + 2] * mul, v[4 * k + 3] * mul);
-    *reinterpret_cast<uint4*>(st_q + lane * 32) = make_uint4(w[0], w[1], w[2], w[3]);
-    *reinterpret_cast<uint4*>(st_q + lane * 32 + 16) = make_uint4(w[4], w[5], w[6], w[7]);
-    if (valid) {
-      const int b = col >> 5;
-      p.q_scale[(static_cast<int64_t>(row >> 7) * p.q_scale_tiles + (b >> 2)) * kScaleTileBytes +
-                mx_scale_tile_offset(static_cast<int>(row & 127), b)] = static_cast<uint8_t>(e);
+    for (int j = 0; j < 4; ++j) {
+      const uint4 t = *reinterpret_cast<const uint4*>(st_tr + lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4));
+      c[4 * j] = t.x, c[4 * j + 1] = t.y, c[4 * j + 2] = t.z, c[4 * j + 3] = t.w;
+    }
+    if (!EXP(2))
+      e_col = quantize_block(c, p.floor_rule, wqt);
+    else {
+      e_col = 0;
+      for (int k = 0; k < 8; ++k) wqt[k] = c[k];
     }
   }
 
-  // ---- columns: through the transpose tile, written column-major (each store instruction puts one column's 32
-  // rows in 64 contiguous bytes, conflict-free), so that a lane reads its column as four 16-byte vectors
-#pragma unroll
-  for (int k = 0; k < 32; ++k)  // bf16-exact values: the top 16 bits are the bf16
-    *reinterpret_cast<uint16_t*>(st_tr + k * 64 + lane * 2) = static_cast<uint16_t>(__float_as_uint(v[k]) >> 16);
-  __syncwarp();
-  {
-    float c[32];
-    float m = 0.f;
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const uint4 t = *reinterpret_cast<const uint4*>(st_tr + lane * 64 + j * 16);
-      const uint32_t w[4] = {t.x, t.y, t.z, t.w};
-#pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        c[8 * j + 2 * k] = __uint_as_float(w[k] << 16);
-        c[8 * j + 2 * k + 1] = __uint_as_float(w[k] & 0xffff0000u);
-      }
-    }
-#pragma unroll
-    for (int r = 0; r < 32; ++r)
-      m = fmaxf(m, fabsf(c[r]));
-    const int e = mx_exponent(__float_as_uint(m), p.floor_rule);
-    const float mul = __uint_as_float(mx_multiplier_bits(e));
-    uint32_t w[8];
-#pragma unroll
-    for (int k = 0; k < 8; ++k)
-      w[k] = e4m3x4(c[4 * k] * mul, c[4 * k + 1] * mul, c[4 * k + 2] * mul, c[4 * k + 3] * mul);
-    *reinterpret_cast<uint4*>(st_qt + lane * 32) = make_uint4(w[0], w[1], w[2], w[3]);
-    *reinterpret_cast<uint4*>(st_qt + lane * 32 + 16) = make_uint4(w[4], w[5], w[6], w[7]);
-    const int n = col + lane;  // row of the transposed layout
-    if (warp_row0 < p.M && n < p.N) {
-      const int b = warp_row0 >> 5;
-      p.qt_scale[(static_cast<int64_t>(n >> 7) * p.qt_scale_tiles + (b >> 2)) * kScaleTileBytes +
-                 mx_scale_tile_offset(n & 127, b)] = static_cast<uint8_t>(e);
-    }
+  STAMP(5);
+  // ---- results out: scale bytes straight to their swizzled positions, data through the staging tiles
+  if (valid && !EXP(4)) {
+    const int b = col >> 5;
+    p.q_scale[(static_cast<int64_t>(row >> 7) * p.q_scale_tiles + (b >> 2)) * kScaleTileBytes +
+              mx_scale_tile_offset(static_cast<int>(row & 127), b)] = static_cast<uint8_t>(e_row);
   }
+  const int n = col + lane;  // row of the transposed layout
+  if (warp_row0 < p.M && n < p.N && !EXP(4)) {
+    const int b = warp_row0 >> 5;
+    p.qt_scale[(static_cast<int64_t>(n >> 7) * p.qt_scale_tiles + (b >> 2)) * kScaleTileBytes +
+               mx_scale_tile_offset(n & 127, b)] = static_cast<uint8_t>(e_col);
+  }
+  STAMP(6);
+  if (lane == 0)
+    tma_store_wait_read<0>();  // the previous chunk's stores have been read out of the staging tiles
+  __syncwarp();
+  STAMP(7);
+  if constexpr (kFuse == kFuseReluSquare) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j)  // h itself leaves as the plain epilogue's output does
+      *reinterpret_cast<uint4*>(st_out + lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4)) =
+            make_uint4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
+  }
+  park_block(wq, st_q, lane);
+  park_block(wqt, st_qt, lane);
+  STAMP(8);
   fence_proxy_async_smem();
   __syncwarp();
-  if (lane == 0 && warp_row0 < p.M && col < p.N) {
+  STAMP(9);
+  if (lane == 0 && warp_row0 < p.M && col < p.N && !EXP(3)) {
     if constexpr (kFuse == kFuseReluSquare)
       tma_store_2d(map_d, st_out, col, warp_row0);
     tma_store_2d(map_q, st_q, col, warp_row0);
     tma_store_2d(map_qt, st_qt, warp_row0, col);
     tma_store_commit();
   }
+  STAMP(10);
 }
 
 // ------------------------------------------------------------------------------------------------ CTA-pair kernel
@@ -1343,7 +1380,7 @@ int make_bytes_map(CUtensorMap* map, void* base, int64_t rows, int64_t cols) {
   const cuuint32_t box[2] = {32, 32};
   const cuuint32_t estr[2] = {1, 1};
   const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, base, dims, strides, box, estr,
-                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_32B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? MXB200_OK : MXB200_ERR_DRIVER;
 }
@@ -1584,6 +1621,11 @@ extern "C" int mxb200_gemm_splitk_static(const void* a, const void* a_scale, con
 }
 
 #ifdef MXB200_TRACE
+extern "C" __attribute__((visibility("default"))) int mxb200_trace_set(int v) {
+  const int zero = 0;
+  cudaMemcpyToSymbol(mxb200::g_chunk_calls, &zero, sizeof(zero));
+  return cudaMemcpyToSymbol(mxb200::g_exp, &v, sizeof(v)) == cudaSuccess ? 0 : 1;
+}
 extern "C" __attribute__((visibility("default"))) int mxb200_trace_read(unsigned long long* out, int n) {
   cudaDeviceSynchronize();
   return cudaMemcpyFromSymbol(out, mxb200::g_trace, sizeof(unsigned long long) * n) == cudaSuccess ? 0 : 1;

@@ -26,6 +26,7 @@
 #include <cuda_bf16.h>
 
 #include "internal.h"
+#include "bf16x2_sm100.cuh"
 #include "mx_common.cuh"
 #include "ptx_sm100.cuh"
 
@@ -87,65 +88,6 @@ __device__ __forceinline__ bool wait_bounded(uint64_t* bar, uint32_t parity, Rin
 
 __device__ __forceinline__ bool wait_bounded_warp(uint64_t* bar, uint32_t parity, RingBarriers* bars, uint32_t site) {
   return __all_sync(0xffffffffu, wait_bounded(bar, parity, bars, site)) != 0;
-}
-
-__device__ __forceinline__ uint32_t add_bf16x2(uint32_t a, uint32_t b) {
-  uint32_t d;
-  asm("add.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
-  return d;
-}
-
-__device__ __forceinline__ uint32_t mul_bf16x2(uint32_t a, uint32_t b) {
-  uint32_t d;
-  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
-  return d;
-}
-
-__device__ __forceinline__ float lo_f32(uint32_t w) {
-  return __uint_as_float(w << 16);
-}
-
-__device__ __forceinline__ float hi_f32(uint32_t w) {
-  return __uint_as_float(w & 0xffff0000u);
-}
-
-__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
-  uint32_t d;
-  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
-  return d;
-}
-
-__device__ __forceinline__ uint32_t cvt_e4m3x4(float a, float b, float c, float d) {
-  uint16_t lo, hi;
-  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %2, %1;" : "=h"(lo) : "f"(a), "f"(b));
-  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %2, %1;" : "=h"(hi) : "f"(c), "f"(d));
-  return static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16);
-}
-
-// e4m3 of four bf16 values (two packed words) times a power of two given as packed bf16. The multiplier is a power
-// of two, so the packed bf16 product equals the fp32 product wherever the result is a normal bf16; below that
-// (|v| < 2^-126) both forms round to zero in e4m3.
-__device__ __forceinline__ uint32_t cvt_e4m3x4_scaled(uint32_t w0, uint32_t w1, uint32_t mul2) {
-  const uint32_t a = mul_bf16x2(w0, mul2), b = mul_bf16x2(w1, mul2);
-  return cvt_e4m3x4(lo_f32(a), hi_f32(a), lo_f32(b), hi_f32(b));
-}
-
-// |x| of two packed bf16 as unsigned 16-bit integers: ordered like the magnitudes, NaN above everything
-__device__ __forceinline__ uint32_t max_abs_u16x2(uint32_t m, uint32_t w) {
-  uint32_t d;
-  asm("max.u16x2 %0, %1, %2;" : "=r"(d) : "r"(m), "r"(w & 0x7fff7fffu));
-  return d;
-}
-
-// max of |x| over packed bf16 magnitudes as the quantizer takes it: fmaxf semantics, so NaN never wins
-__device__ __forceinline__ float amax_from_packed(uint32_t m, const uint32_t* words, int count) {
-  const uint32_t lo = m & 0xffffu, hi = m >> 16;
-  if (max(lo, hi) <= 0x7f80u)
-    return __uint_as_float(max(lo, hi) << 16);
-  float f = 0.f;  // a NaN among them: redo with fmaxf, which skips NaN
-  for (int k = 0; k < count; ++k)
-    f = fmaxf(f, fmaxf(fabsf(lo_f32(words[k])), fabsf(hi_f32(words[k]))));
-  return f;
 }
 
 template <int kIters>
@@ -226,7 +168,7 @@ __global__ void __launch_bounds__(kThreads, 1) mxb200_residual_norm_mx_kernel(co
   }
 
   // ---- consumers
-  const uint32_t lr2 = blend ? pack_bf16x2(*a.lr, *a.lr) : 0u, l02 = blend ? pack_bf16x2(*a.l0, *a.l0) : 0u;
+  const uint32_t lr2 = blend ? pack_bf16x2_rn(*a.lr, *a.lr) : 0u, l02 = blend ? pack_bf16x2_rn(*a.l0, *a.l0) : 0u;
   auto* out = static_cast<unsigned char*>(a.out.data);
   auto* out_scale = static_cast<unsigned char*>(a.out.scale);
   auto* out_t = static_cast<unsigned char*>(a.out_t.data);
@@ -310,7 +252,7 @@ __global__ void __launch_bounds__(kThreads, 1) mxb200_residual_norm_mx_kernel(co
           const uint32_t src[4] = {nv[it].x, nv[it].y, nv[it].z, nv[it].w};
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
-            w[k] = pack_bf16x2(lo_f32(src[k]) * rstd, hi_f32(src[k]) * rstd);
+            w[k] = pack_bf16x2_rn(lo_f32(src[k]) * rstd, hi_f32(src[k]) * rstd);
             m = max_abs_u16x2(m, w[k]);
           }
           tile_row[it * 32] = make_uint4(w[0], w[1], w[2], w[3]);
@@ -334,8 +276,8 @@ __global__ void __launch_bounds__(kThreads, 1) mxb200_residual_norm_mx_kernel(co
           const int e = mx_exponent(__float_as_uint(amax), false);
           const uint32_t mul2 = (mx_multiplier_bits(e) >> 16) * 0x10001u;
           uint2 o;
-          o.x = cvt_e4m3x4_scaled(w[0], w[1], mul2);
-          o.y = cvt_e4m3x4_scaled(w[2], w[3], mul2);
+          o.x = e4m3x4_scaled(w[0], w[1], mul2);
+          o.y = e4m3x4_scaled(w[2], w[3], mul2);
           out_row[it * 32] = o;
           if ((lane & 3) == 0)
             scale_row[it * 2 * kScaleTileBytes] = static_cast<unsigned char>(e);
@@ -368,7 +310,7 @@ __global__ void __launch_bounds__(kThreads, 1) mxb200_residual_norm_mx_kernel(co
       uint32_t q[8];
 #pragma unroll
       for (int k = 0; k < 8; ++k)
-        q[k] = cvt_e4m3x4_scaled(w[2 * k], w[2 * k + 1], mul2);
+        q[k] = e4m3x4_scaled(w[2 * k], w[2 * k + 1], mul2);
       unsigned char* dst = out_t + static_cast<int64_t>(c) * a.out_t.ld + row0;
       if (p.wide_out_t) {
         asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(dst), "r"(q[0]), "r"(q[1]), "r"(q[2]),

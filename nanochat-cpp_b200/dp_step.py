@@ -184,7 +184,7 @@ class DpStep:
         self.dx_lm = torch.empty((M, C), dtype=bf, device=device)
 
         self.bucket = GradBucket(cfg, device, world)
-        self.comm_stream = torch.cuda.Stream(device=device) if device.type == "cuda" else None
+        self.comm_stream = torch.cuda.Stream(device=device) if (device.type == "cuda" and world > 1) else None
         self._pending: list = []
 
     # ------------------------------------------------------------------ pieces

@@ -20,7 +20,7 @@ __all__ = [
     "Fp8Tensor", "Fp8WeightCache", "MxGemmBackend", "set_mx_gemm_backend", "mx_gemm_backend", "mx_fits",
     "empty_mx", "empty_mx_scale", "mx_out", "mx_outs", "quantize_mx", "quantize_mx_into",
     "quantize_mx_relu_square_bwd", "residual_norm_mx", "residual_norm_mx_fits", "quantize_fp8_weight", "mx_qkv_weights", "mx_gemm", "mx_gemm_out",
-    "mx_gemm_f32", "mx_gemm_relu_square", "mx_gemm_relu_square_bwd", "mx_grad_direct", "mx_grad_weights", "fp8_matmul", "fp8_eligible",
+    "mx_gemm_f32", "mx_gemm_relu_square", "mx_gemm_relu_square_bwd", "mx_grad_direct", "mx_grad_weights", "fp8_matmul", "fp8_qkv", "fp8_relu_square_mlp", "relu_square_mlp_mx", "fp8_eligible",
     "SCALE_REFERENCE", "SCALE_OCP_FLOOR",
 ]
 
@@ -443,6 +443,125 @@ class _Float8Matmul(torch.autograd.Function):
             return dx, None, None
         dw = mx_gemm(gq.data_t, gq.inv_scale_t, x_t, x_scale_t, torch.float32)
         return dx, dw.to(ctx.w.dtype), None
+
+
+class _MxQkv(torch.autograd.Function):
+    """q, k, v = x . w_i^T with x quantized once and one GEMM each for the forward, the input gradient and the weight
+    gradients: MX scales run along K, so the three weights concatenate along their rows and the three output
+    gradients along their columns (src/nanochat/model/fp8/fp8.cpp:424-462)."""
+
+    @staticmethod
+    def forward(ctx, x, wq, wk, wv, gate_cols, cache):
+        sizes = (wq.size(0), wk.size(0), wv.size(0))
+        xq = quantize_mx(x)
+        w, w_t, w_scale, w_scale_t = mx_qkv_weights(wq, wk, wv, cache)
+        qkv = mx_gemm(xq.data, xq.inv_scale, w, w_scale, torch.bfloat16)
+        ctx.save_for_backward(xq.data_t, xq.inv_scale_t, w_t, w_scale_t)
+        ctx.ws, ctx.gate_cols, ctx.sizes = (wq, wk, wv), gate_cols, sizes
+        ctx.direct = all(mx_grad_direct(t) for t in (wq, wk, wv))
+        out = [qkv.narrow(1, 0, sizes[0]), qkv.narrow(1, sizes[0], sizes[1]), qkv.narrow(1, sizes[0] + sizes[1], sizes[2])]
+        if gate_cols > 0:
+            out.append(x.narrow(1, 0, gate_cols).contiguous())
+        return tuple(out)
+
+    @staticmethod
+    def backward(ctx, *grads):
+        x_t, x_scale_t, w_t, w_scale_t = ctx.saved_tensors
+        N, sizes = x_t.size(1), ctx.sizes
+        n = sum(sizes)
+        dev = x_t.device
+        g = torch.empty((N, n), dtype=E4M3, device=dev)
+        g_t = torch.empty((n, N), dtype=E4M3, device=dev)
+        g_scale, g_scale_t = empty_mx_scale(N, n, dev), empty_mx_scale(n, N, dev)
+        row = 0
+        for i in range(3):
+            gi = grads[i] if grads[i] is not None else torch.zeros((N, sizes[i]), dtype=torch.bfloat16, device=dev)
+            quantize_mx_into(gi.contiguous(), False, mx_out(g, g_scale, 0, row), mx_out(g_t, g_scale_t, row, 0))
+            row += sizes[i]
+        dx = mx_gemm(g, g_scale, w_t, w_scale_t, torch.bfloat16)
+        if ctx.gate_cols > 0 and grads[3] is not None:
+            dx.narrow(1, 0, ctx.gate_cols).add_(grads[3])
+        if ctx.direct:
+            mx_grad_weights(g_t, g_scale_t, x_t, x_scale_t, list(ctx.ws))
+            return dx, None, None, None, None, None
+        dw = mx_gemm(g_t, g_scale_t, x_t, x_scale_t, torch.float32)
+        parts, row = [], 0
+        for w, rows in zip(ctx.ws, sizes):
+            parts.append(dw.narrow(0, row, rows).to(w.dtype))
+            row += rows
+        return (dx, *parts, None, None)
+
+
+def fp8_qkv(x_2d: torch.Tensor, wq: torch.Tensor, wk: torch.Tensor, wv: torch.Tensor, gate_cols: int = 0,
+            cache: Optional[Fp8WeightCache] = None):
+    """Attention's c_q, c_k, c_v as fp8_matmuls of the same x_2d (N, in) bf16, merged
+    (src/nanochat/model/fp8/fp8.h:58-66, MX branch). Returns (q, k, v), views of one (N, q + k + v) buffer, plus
+    x_2d[:, :gate_cols] when gate_cols > 0 (the value-embedding gate's input; its gradient is added to dx in the
+    same pass)."""
+    n = wq.size(0) + wk.size(0) + wv.size(0)
+    if not (mx_fits(x_2d.size(0), x_2d.size(1)) and n % 128 == 0 and all(w.size(0) % 128 == 0 for w in (wq, wk, wv))
+            and 0 <= gate_cols <= x_2d.size(1)):
+        raise RuntimeError("fp8_qkv: MX needs N, in and every weight's rows % 128")
+    return _MxQkv.apply(x_2d.contiguous(), wq, wk, wv, gate_cols, cache)
+
+
+class _Fp8ReluSquareMlp(torch.autograd.Function):
+    """c_proj(relu(c_fc(x))^2) as two MX Linears with relu^2 folded into the GEMM epilogues: the forward quantizes
+    relu(h)^2 in c_fc's epilogue, the backward quantizes dh = (go . w_proj) * 2h in the dgrad GEMM's epilogue without
+    writing it; h is what is saved (src/nanochat/model/fp8/fp8.cpp:262-338, MX branch)."""
+
+    @staticmethod
+    def forward(ctx, x, w_fc, w_proj, fc_cache, proj_cache, x_mx):
+        xq = x_mx if x_mx is not None else quantize_mx(x)
+        fcq = quantize_fp8_weight(w_fc, fc_cache)
+        h = torch.empty((x.size(0), w_fc.size(0)), dtype=torch.bfloat16, device=x.device)
+        aq = empty_mx(h.size(0), h.size(1), h.device)
+        mx_gemm_relu_square(h, aq.data, aq.inv_scale, aq.data_t, aq.inv_scale_t, xq.data, xq.inv_scale, fcq.data,
+                            fcq.inv_scale)
+        projq = quantize_fp8_weight(w_proj, proj_cache)
+        ctx.save_for_backward(xq.data_t, xq.inv_scale_t, fcq.data_t, fcq.inv_scale_t, h, aq.data_t, aq.inv_scale_t,
+                              projq.data_t, projq.inv_scale_t)
+        ctx.w_fc, ctx.w_proj = w_fc, w_proj
+        return mx_gemm(aq.data, aq.inv_scale, projq.data, projq.inv_scale, torch.bfloat16)
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        x_t, x_scale_t, fc_t, fc_scale_t, h, a_t, a_scale_t, proj_t, proj_scale_t = ctx.saved_tensors
+        go = quantize_mx(grad_output.contiguous())
+
+        def weight_grad(g_t, g_scale_t, in_t, in_scale_t, w):
+            if mx_grad_direct(w):
+                mx_grad_weights(g_t, g_scale_t, in_t, in_scale_t, [w])
+                return None
+            return mx_gemm(g_t, g_scale_t, in_t, in_scale_t, torch.float32).to(w.dtype)
+
+        grad_proj = weight_grad(go.data_t, go.inv_scale_t, a_t, a_scale_t, ctx.w_proj)
+        dhq = empty_mx(h.size(0), h.size(1), h.device)
+        mx_gemm_relu_square_bwd(go.data, go.inv_scale, proj_t, proj_scale_t, h, dhq.data, dhq.inv_scale, dhq.data_t,
+                                dhq.inv_scale_t)
+        grad_x = mx_gemm(dhq.data, dhq.inv_scale, fc_t, fc_scale_t, torch.bfloat16)
+        grad_fc = weight_grad(dhq.data_t, dhq.inv_scale_t, x_t, x_scale_t, ctx.w_fc)
+        return grad_x, grad_fc, grad_proj, None, None, None
+
+
+def relu_square_mlp_mx(N: int, cin: int, w_fc: torch.Tensor, w_proj: torch.Tensor) -> bool:
+    """Whether fp8_relu_square_mlp of an (N, in) input runs under MX: every dim % 128
+    (src/nanochat/model/fp8/fp8.h:56-58)."""
+    return (mx_fits(N, cin) and mx_fits(w_fc.size(0), w_fc.size(1)) and mx_fits(w_proj.size(0), w_proj.size(1))
+            and w_fc.size(1) == cin and w_proj.size(1) == w_fc.size(0))
+
+
+def fp8_relu_square_mlp(x_2d: torch.Tensor, w_fc: torch.Tensor, w_proj: torch.Tensor,
+                        fc_cache: Optional[Fp8WeightCache] = None, proj_cache: Optional[Fp8WeightCache] = None,
+                        x_mx: Optional[Fp8Tensor] = None) -> torch.Tensor:
+    """The MLP's c_proj(relu(c_fc(x)).square()) with both matmuls as fp8_matmul, bit for bit
+    (src/nanochat/model/fp8/fp8.h:46-54). x_2d (N, in) bf16, w_fc (hidden, in), w_proj (out, hidden) -> (N, out).
+    x_mx: x_2d already quantized in both layouts (residual_norm_mx); x_2d then only carries autograd."""
+    if not relu_square_mlp_mx(x_2d.size(0), x_2d.size(1), w_fc, w_proj):
+        raise RuntimeError("fp8_relu_square_mlp: MX needs N, in, hidden, out % 128")
+    if x_mx is not None and (x_mx.data is None or x_mx.data_t is None):
+        raise RuntimeError("fp8_relu_square_mlp: x_mx needs both layouts")
+    return _Fp8ReluSquareMlp.apply(x_2d.contiguous(), w_fc, w_proj, fc_cache, proj_cache, x_mx)
 
 
 def fp8_matmul(input_2d: torch.Tensor, weight: torch.Tensor, cache: Optional[Fp8WeightCache] = None) -> torch.Tensor:
