@@ -73,6 +73,24 @@ MXB200_API int mxb200_quantize_mx(const void* x, int x_bf16, int64_t rows, int64
 MXB200_API int mxb200_quantize_mx_relu_square_bwd(const void* g, const void* h, int64_t rows, int64_t cols, mxb200_mx_out out,
                                        mxb200_mx_out out_t, int scale_rule, void* stream);
 
+/* Loss pass of the chunked lm_head: replaces nanochat::kernels::softcap_ce with grad = false
+ * (src/nanochat/model/ops/softcap_ce_kernel.h:13-22), the form the MX branch uses (ops/softcap_ce.cpp:66-71).
+ * logits: (rows, ld) bf16, columns [0, padded) used, columns >= vocab ignored; padded, ld % 8 == 0. targets: (rows)
+ * int64 on the device, < 0 = ignored. With capped = softcap * tanh(z / softcap): lse[row] = log sum exp(capped)
+ * (unset for ignored rows), loss[row] = lse - capped[target] (0 for ignored rows). loss or lse may be null. */
+MXB200_API int mxb200_softcap_ce_loss(const void* logits, int64_t rows, int64_t ld, const int64_t* targets, int vocab,
+                                      int padded, float softcap, float* loss, float* lse, void* stream);
+
+/* Replaces nanochat::kernels::softcap_ce_grad_mx (softcap_ce_kernel.h:24-29; kernel nanochat_softcap_ce_grad_mx,
+ * softcap_ce_kernel.cu:118-176): the loss's gradient with respect to the logits, as the bf16 the reference's grad
+ * kernel would write, g = bf16((softmax(capped) - onehot(target)) * (1 - tanh^2) * scale), MX-quantized in both
+ * layouts without being written. scale = grad_scale[row * grad_scale_stride] (null: 1) / *num_valid (null: 1), both
+ * on the device; rows with target < 0 and columns >= vocab give 0. rows, padded % 128 == 0. */
+MXB200_API int mxb200_softcap_ce_grad_mx(const void* logits, int64_t rows, int64_t ld, const int64_t* targets,
+                                         const float* lse, int vocab, int padded, float softcap,
+                                         const float* grad_scale, int64_t grad_scale_stride, const int64_t* num_valid,
+                                         mxb200_mx_out out, mxb200_mx_out out_t, int scale_rule, void* stream);
+
 /* Arguments of mxb200_residual_norm_mx_fwd; the fields of nanochat::kernels::ResidualNormMxFwd and its base
  * ResidualNormFwd (src/nanochat/model/ops/residual_norm_kernel.h:17-41) in one flat struct. All tensors are
  * (rows, cols) contiguous bf16 unless noted, 16-byte aligned. */

@@ -143,4 +143,26 @@ inline void residual_norm_mx_fwd(const ResidualNormMxFwd& a, cudaStream_t stream
   b200_detail::status_slot() = mxb200_residual_norm_mx_fwd(&args, stream);
 }
 
+// src/nanochat/model/ops/softcap_ce_kernel.h:13-22, the form the MX branch calls (grad = false: loss and lse only; the
+// gradient then comes from softcap_ce_grad_mx). A call with grad = true is refused (MXB200_ERR_ARGUMENT in
+// last_status()): writing the bf16 gradient belongs to the recipes this library does not replace.
+inline void softcap_ce(void* logits, int64_t rows, int64_t ld, const int64_t* targets, int vocab, int padded,
+                       float softcap, float* loss, const float* /*grad_scale*/, int64_t /*grad_scale_stride*/,
+                       const int64_t* /*num_valid*/, bool grad, float* /*grad_amax*/, float* lse, cudaStream_t stream) {
+  b200_detail::status_slot() =
+        grad ? MXB200_ERR_ARGUMENT
+             : mxb200_softcap_ce_loss(logits, rows, ld, targets, vocab, padded, softcap, loss, lse, stream);
+}
+
+// src/nanochat/model/ops/softcap_ce_kernel.h:24-29
+inline void softcap_ce_grad_mx(const void* logits, int64_t rows, int64_t ld, const int64_t* targets, const float* lse,
+                               int vocab, int padded, float softcap, const float* grad_scale,
+                               int64_t grad_scale_stride, const int64_t* num_valid, MxOut out, MxOut out_t,
+                               cudaStream_t stream) {
+  b200_detail::status_slot() =
+        mxb200_softcap_ce_grad_mx(logits, rows, ld, targets, lse, vocab, padded, softcap, grad_scale, grad_scale_stride,
+                                  num_valid, b200_detail::view(out), b200_detail::view(out_t), MXB200_SCALE_REFERENCE,
+                                  stream);
+}
+
 }  // namespace nanochat::kernels

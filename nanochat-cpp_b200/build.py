@@ -17,7 +17,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libmxb200.so")
-SOURCES = ["capi.cu", "quantize_sm100.cu", "residual_norm_sm100.cu", "gemm_sm100.cu"]
+SOURCES = ["capi.cu", "quantize_sm100.cu", "residual_norm_sm100.cu", "softcap_ce_sm100.cu", "gemm_sm100.cu"]
 FLAGS = ["-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
          "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "--cudart", "static"]
 

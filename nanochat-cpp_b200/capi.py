@@ -22,6 +22,7 @@ STATIC_SCRATCH_BYTES = 32 << 20
 SYMBOLS = (
     "mxb200_quantize_mx", "mxb200_quantize_mx_relu_square_bwd", "mxb200_gemm_bf16", "mxb200_gemm_f32",
     "mxb200_gemm_relu_square", "mxb200_gemm_relu_square_bwd", "mxb200_residual_norm_mx_fwd",
+    "mxb200_softcap_ce_loss", "mxb200_softcap_ce_grad_mx",
     "mxb200_gemm_splits", "mxb200_gemm_workspace_bytes", "mxb200_gemm_splitk", "mxb200_gemm_splitk_static",
     "mxb200_strerror",
     "mxb200_device_status", "mxb200_set_gemm_config", "mxb200_launch_count", "mxb200_version",
@@ -61,6 +62,9 @@ def _load() -> ctypes.CDLL:
     lib.mxb200_gemm_relu_square.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, i64, i64, i64, vp]
     lib.mxb200_gemm_relu_square_bwd.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, i64, i64, i64, vp]
     lib.mxb200_residual_norm_mx_fwd.argtypes = [ctypes.POINTER(ResidualNormMx), vp]
+    f32 = ctypes.c_float
+    lib.mxb200_softcap_ce_loss.argtypes = [vp, i64, i64, vp, i32, i32, f32, vp, vp, vp]
+    lib.mxb200_softcap_ce_grad_mx.argtypes = [vp, i64, i64, vp, vp, i32, i32, f32, vp, i64, vp, MxOut, MxOut, i32, vp]
     lib.mxb200_gemm_splits.argtypes = [i64, i64, i64]
     lib.mxb200_gemm_workspace_bytes.argtypes = [i64, i64, i64, i32]
     lib.mxb200_gemm_workspace_bytes.restype = ctypes.c_size_t

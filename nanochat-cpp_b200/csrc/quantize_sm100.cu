@@ -26,7 +26,19 @@ namespace {
 constexpr int kTile = 128;
 constexpr int kThreads = 256;
 
-enum Prologue : int { kNone = 0, kReluSquare = 1, kReluSquareBwd = 2 };
+enum Prologue : int { kNone = 0, kReluSquare = 1, kReluSquareBwd = 2, kSoftcapGrad = 3 };
+
+// The softcap cross-entropy gradient prologue's inputs (src/nanochat/model/ops/softcap_ce_kernel.cu:118-145): x holds
+// the chunk's logits, and per row a target, the log-sum-exp of its capped logits and an upstream scale.
+struct SoftcapGrad {
+  const int64_t* targets;
+  const float* lse;
+  const float* grad_scale;
+  int64_t grad_scale_stride;
+  const int64_t* num_valid;
+  int vocab;
+  float softcap;
+};
 
 struct QuantParams {
   const void* x;
@@ -37,7 +49,16 @@ struct QuantParams {
   bool floor_rule;
   bool wide_in;     // x is 32-byte aligned
   bool wide_out_t;  // out_t.data and its ld are 32-byte aligned
+  SoftcapGrad ce;   // softcap gradient prologue only
 };
+
+// d loss_row / d z of one logit, before rounding: p = softmax of the capped logits, th = tanh(z / softcap). The
+// expressions are the reference's (softcap_ce_kernel.cu:49-54), so the compiler contracts them the same way.
+__device__ __forceinline__ float softcap_ce_grad(float z, bool is_target, float lse, float softcap, float scale) {
+  const float th = tanhf(z / softcap);
+  const float p = expf(softcap * th - lse);
+  return (p - (is_target ? 1.f : 0.f)) * (1.f - th * th) * scale;
+}
 
 __device__ __forceinline__ float bf16_round(float v) {
   return __bfloat162float(__float2bfloat16(v));
@@ -115,7 +136,8 @@ __device__ __forceinline__ void load_u32x8_stream(const void* p, uint32_t (&w)[8
 // Row pass: a thread owns 16 consecutive values of a row (one 256-bit load of bf16), two lanes share a 32-value
 // block (one shuffle), 16 E4M3 bytes leave with one 128-bit store (512 contiguous bytes per warp).
 template <bool kIn32, int kPro>
-__global__ void __launch_bounds__(kThreads, kIn32 ? 2 : (kPro == kReluSquareBwd ? 3 : 4)) mxb200_quantize_kernel(const QuantParams p) {
+__global__ void __launch_bounds__(kThreads, (kIn32 || kPro == kSoftcapGrad) ? 2 : (kPro == kReluSquareBwd ? 3 : 4))
+      mxb200_quantize_kernel(const QuantParams p) {
   using Park = typename std::conditional<kIn32, float, __nv_bfloat16>::type;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   Park* tile = reinterpret_cast<Park*>(smem_raw);                               // [128][128]
@@ -194,13 +216,37 @@ __global__ void __launch_bounds__(kThreads, kIn32 ? 2 : (kPro == kReluSquareBwd 
       } else {
         float m = 0.f;
         uint32_t pk[8];
+        if constexpr (kPro == kSoftcapGrad) {
+          // the gradient as the reference's grad kernel would have written it in bf16: 0 for ignored rows and for
+          // the padding columns
+          const int64_t grow = row0 + r;
+          const int64_t target = p.ce.targets[grow];
+          if (target < 0) {
 #pragma unroll
-        for (int k = 0; k < 16; ++k) {
-          float hv = 0.f;
-          if constexpr (kPro == kReluSquareBwd)
-            hv = (k & 1) ? __uint_as_float(rawh[it][k >> 1] & 0xffff0000u) : __uint_as_float(rawh[it][k >> 1] << 16);
-          v[k] = prologue<kPro>(v[k], hv);
-          m = fmaxf(m, fabsf(v[k]));
+            for (int k = 0; k < 16; ++k)
+              v[k] = 0.f;
+          } else {
+            const float lse = p.ce.lse[grow];
+            float scale = p.ce.grad_scale != nullptr ? p.ce.grad_scale[grow * p.ce.grad_scale_stride] : 1.f;
+            if (p.ce.num_valid != nullptr)
+              scale /= static_cast<float>(*p.ce.num_valid);
+            const int64_t gcol = col0 + c;
+#pragma unroll
+            for (int k = 0; k < 16; ++k) {
+              const float g = gcol + k < p.ce.vocab ? softcap_ce_grad(v[k], gcol + k == target, lse, p.ce.softcap, scale) : 0.f;
+              v[k] = bf16_round(g);
+              m = fmaxf(m, fabsf(v[k]));
+            }
+          }
+        } else {
+#pragma unroll
+          for (int k = 0; k < 16; ++k) {
+            float hv = 0.f;
+            if constexpr (kPro == kReluSquareBwd)
+              hv = (k & 1) ? __uint_as_float(rawh[it][k >> 1] & 0xffff0000u) : __uint_as_float(rawh[it][k >> 1] << 16);
+            v[k] = prologue<kPro>(v[k], hv);
+            m = fmaxf(m, fabsf(v[k]));
+          }
         }
         m_bits = __float_as_uint(m);
 #pragma unroll
@@ -336,7 +382,8 @@ int launch(const QuantParams& p, int64_t tiles, cudaStream_t stream) {
 }
 
 int quantize(const void* x, const void* h, bool x_bf16, int64_t rows, int64_t cols, mxb200_mx_out out,
-             mxb200_mx_out out_t, int pro, int scale_rule, void* stream) {
+             mxb200_mx_out out_t, int pro, int scale_rule, void* stream, const SoftcapGrad* ce = nullptr,
+             int64_t ld = 0) {
   DeviceInfo dev;
   if (int s = current_device(&dev); s != MXB200_OK)
     return s;
@@ -356,9 +403,15 @@ int quantize(const void* x, const void* h, bool x_bf16, int64_t rows, int64_t co
     return s;
   if (out.data == nullptr && out_t.data == nullptr)
     return MXB200_OK;
-  QuantParams p{x, h, cols, out, out_t, static_cast<int>(cols / kTile), scale_rule == MXB200_SCALE_OCP_FLOOR,
-                (reinterpret_cast<uintptr_t>(x) & 31u) == 0,
-                (reinterpret_cast<uintptr_t>(out_t.data) & 31u) == 0 && out_t.ld % 32 == 0};
+  if (ld == 0)
+    ld = cols;
+  if (ld < cols || ld % 8 != 0)
+    return MXB200_ERR_SHAPE;
+  QuantParams p{x, h, ld, out, out_t, static_cast<int>(cols / kTile), scale_rule == MXB200_SCALE_OCP_FLOOR,
+                (reinterpret_cast<uintptr_t>(x) & 31u) == 0 && ld % 16 == 0,
+                (reinterpret_cast<uintptr_t>(out_t.data) & 31u) == 0 && out_t.ld % 32 == 0, SoftcapGrad{}};
+  if (ce != nullptr)
+    p.ce = *ce;
   const int64_t tiles = (rows / kTile) * (cols / kTile);
   auto* s = static_cast<cudaStream_t>(stream);
   if (!x_bf16)
@@ -370,6 +423,8 @@ int quantize(const void* x, const void* h, bool x_bf16, int64_t rows, int64_t co
       return launch<false, kReluSquare>(p, tiles, s);
     case kReluSquareBwd:
       return launch<false, kReluSquareBwd>(p, tiles, s);
+    case kSoftcapGrad:
+      return ce != nullptr ? launch<false, kSoftcapGrad>(p, tiles, s) : MXB200_ERR_NULL;
     default:
       return MXB200_ERR_ARGUMENT;
   }
@@ -390,4 +445,17 @@ extern "C" int mxb200_quantize_mx_relu_square_bwd(const void* g, const void* h, 
                                                   mxb200_mx_out out, mxb200_mx_out out_t, int scale_rule,
                                                   void* stream) {
   return mxb200::quantize(g, h, true, rows, cols, out, out_t, mxb200::kReluSquareBwd, scale_rule, stream);
+}
+
+extern "C" int mxb200_softcap_ce_grad_mx(const void* logits, int64_t rows, int64_t ld, const int64_t* targets,
+                                         const float* lse, int vocab, int padded, float softcap,
+                                         const float* grad_scale, int64_t grad_scale_stride, const int64_t* num_valid,
+                                         mxb200_mx_out out, mxb200_mx_out out_t, int scale_rule, void* stream) {
+  if (targets == nullptr || lse == nullptr)
+    return MXB200_ERR_NULL;
+  if (vocab <= 0 || vocab > padded || !(softcap > 0.f))
+    return MXB200_ERR_ARGUMENT;
+  const mxb200::SoftcapGrad ce{targets, lse, grad_scale, grad_scale_stride, num_valid, vocab, softcap};
+  return mxb200::quantize(logits, nullptr, true, rows, padded, out, out_t, mxb200::kSoftcapGrad, scale_rule, stream,
+                          &ce, ld);
 }

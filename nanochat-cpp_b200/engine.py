@@ -21,6 +21,7 @@ __all__ = [
     "empty_mx", "empty_mx_scale", "mx_out", "mx_outs", "quantize_mx", "quantize_mx_into",
     "quantize_mx_relu_square_bwd", "residual_norm_mx", "residual_norm_mx_fits", "quantize_fp8_weight", "mx_qkv_weights", "mx_gemm", "mx_gemm_out",
     "mx_gemm_f32", "mx_gemm_relu_square", "mx_gemm_relu_square_bwd", "mx_grad_direct", "mx_grad_weights", "fp8_matmul", "fp8_qkv", "fp8_relu_square_mlp", "relu_square_mlp_mx", "fp8_eligible",
+    "softcap_ce_loss", "softcap_ce_grad_mx", "softcap_cross_entropy",
     "SCALE_REFERENCE", "SCALE_OCP_FLOOR",
 ]
 
@@ -571,3 +572,155 @@ def fp8_matmul(input_2d: torch.Tensor, weight: torch.Tensor, cache: Optional[Fp8
     if not (mx_fits(input_2d.size(0), input_2d.size(1)) and mx_fits(weight.size(0), weight.size(1))):
         raise RuntimeError("fp8_matmul: MX needs N, in, out % 128")
     return _Float8Matmul.apply(input_2d.contiguous(), weight, cache)
+
+
+# ------------------------------------------------------------------------------------------------ chunked lm_head loss
+
+def softcap_ce_loss(logits: torch.Tensor, targets: torch.Tensor, vocab: int, softcap: float,
+                    loss: Optional[torch.Tensor] = None, lse: Optional[torch.Tensor] = None):
+    """Per row of bf16 logits (rows, padded): lse of the soft-capped logits and loss = lse - capped[target]; rows with
+    target < 0 get loss 0 (src/nanochat/model/ops/softcap_ce_kernel.h:13-22 with grad = false). Returns (loss, lse),
+    written into the given fp32 tensors when present."""
+    _require_cuda(logits, "softcap_ce_loss")
+    rows, padded = logits.shape
+    if not (logits.dtype == torch.bfloat16 and logits.stride(1) == 1 and targets.dtype == torch.int64
+            and targets.is_contiguous() and targets.numel() == rows):
+        raise RuntimeError("softcap_ce_loss: expected bf16 logits (rows, padded) and int64 targets (rows)")
+    loss = torch.empty(rows, dtype=torch.float32, device=logits.device) if loss is None else loss
+    lse = torch.empty(rows, dtype=torch.float32, device=logits.device) if lse is None else lse
+    check(lib.mxb200_softcap_ce_loss(logits.data_ptr(), rows, logits.stride(0), targets.data_ptr(), vocab, padded,
+                                     softcap, loss.data_ptr(), lse.data_ptr(), _stream()), "softcap_ce_loss")
+    return loss, lse
+
+
+def softcap_ce_grad_mx(logits: torch.Tensor, targets: torch.Tensor, lse: torch.Tensor, vocab: int, softcap: float,
+                       out: MxOut, out_t: MxOut, grad_scale: Optional[torch.Tensor] = None,
+                       num_valid: Optional[torch.Tensor] = None, scale_rule: int = SCALE_REFERENCE) -> None:
+    """The loss's gradient with respect to the logits, MX-quantized (as quantize_mx of its bf16) into out / out_t
+    without being written, from the logits and softcap_ce_loss's lse
+    (src/nanochat/model/ops/softcap_ce_kernel.h:24-29). grad_scale: fp32 (rows) or one element (every row);
+    num_valid: int64 scalar on the device that divides the scale."""
+    _require_cuda(logits, "softcap_ce_grad_mx")
+    rows, padded = logits.shape
+    stride = 0
+    if grad_scale is not None:
+        if grad_scale.dtype != torch.float32 or not grad_scale.is_contiguous():
+            raise RuntimeError("softcap_ce_grad_mx: grad_scale must be contiguous fp32")
+        stride = 1 if grad_scale.dim() == 1 and grad_scale.numel() == rows and rows > 1 else 0
+    if num_valid is not None and num_valid.dtype != torch.int64:
+        raise RuntimeError("softcap_ce_grad_mx: num_valid must be int64")
+    check(lib.mxb200_softcap_ce_grad_mx(logits.data_ptr(), rows, logits.stride(0), targets.data_ptr(), lse.data_ptr(),
+                                        vocab, padded, softcap,
+                                        grad_scale.data_ptr() if grad_scale is not None else None, stride,
+                                        num_valid.data_ptr() if num_valid is not None else None, out, out_t,
+                                        scale_rule, _stream()), "softcap_ce_grad_mx")
+
+
+def _run_chunks(x, weight, targets, vocab, softcap, chunk_rows, losses, grad_x, grad_scale, num_valid, cache):
+    """The MX branch of the reference's run_chunks (src/nanochat/model/ops/softcap_ce.cpp:27-110): per chunk of rows
+    logits = xq[chunk] . wq^T, the loss pass, the gradient quantized straight from the logits (row-wise into a chunk
+    buffer, transposed into one (padded, N) buffer), grad_x[chunk] = gq . wq_t^T. Returns (xq, g_all) whose transposes
+    are the operands of the single weight-gradient GEMM, or (None, None) without grad_x."""
+    N, C = x.shape
+    padded = weight.size(0)
+    grad = grad_x is not None
+    xq = quantize_mx(x, True, grad)
+    wq = quantize_fp8_weight(weight, cache)
+    rows_max = min(N, chunk_rows)
+    logits = torch.empty((rows_max, padded), dtype=torch.bfloat16, device=x.device)
+    lse = torch.empty(rows_max, dtype=torch.float32, device=x.device)
+    loss_scratch = torch.empty(rows_max, dtype=torch.float32, device=x.device) if losses is None else None
+    g_all = empty_mx(N, padded, x.device, False, True) if grad else None
+    blocks = C // 32
+    for begin in range(0, N, chunk_rows):
+        end = min(N, begin + chunk_rows)
+        rows = end - begin
+        buf = logits[:rows]
+        mx_gemm_out(buf, xq.data[begin:end], xq.inv_scale[begin * blocks:end * blocks], wq.data, wq.inv_scale)
+        softcap_ce_loss(buf, targets[begin:end], vocab, softcap,
+                        losses[begin:end] if losses is not None else loss_scratch[:rows], lse[:rows])
+        if not grad:
+            continue
+        gq = empty_mx(rows, padded, x.device, True, False)
+        scale = None
+        if grad_scale is not None:
+            scale = grad_scale[begin:end] if grad_scale.dim() == 1 and grad_scale.numel() == N else grad_scale
+        softcap_ce_grad_mx(buf, targets[begin:end], lse[:rows], vocab, softcap, mx_out(gq.data, gq.inv_scale, 0, 0),
+                           mx_out(g_all.data_t, g_all.inv_scale_t, 0, begin), scale, num_valid)
+        mx_gemm_out(grad_x[begin:end], gq.data, gq.inv_scale, wq.data_t, wq.inv_scale_t)
+    return (xq, g_all) if grad else (None, None)
+
+
+class _SoftcapCrossEntropy(torch.autograd.Function):
+    """src/nanochat/model/ops/softcap_ce.cpp:118-205, MX branch: for mean/sum the incoming gradient is a scalar, so the
+    forward computes grad_x and the weight gradient's operands at once and the backward only scales (one GEMM with
+    alpha = the incoming gradient, straight into .grad when the weight is an fp32 leaf); for none the backward re-runs
+    the chunks with the per-row gradient."""
+
+    @staticmethod
+    def forward(ctx, x, weight, targets, vocab, softcap, chunk_rows, reduction, needs_grad, cache):
+        num_valid = (targets >= 0).sum()
+        losses = torch.empty(x.size(0), dtype=torch.float32, device=x.device)
+        precompute = needs_grad and reduction != "none"
+        grad_x = torch.empty_like(x) if precompute else None
+        xq, g_all = _run_chunks(x, weight, targets, vocab, softcap, chunk_rows, losses, grad_x, None,
+                                num_valid if reduction == "mean" else None, cache)
+        ctx.precomputed, ctx.weight = precompute, weight
+        ctx.args = (vocab, softcap, chunk_rows, cache)
+        if precompute:
+            ctx.save_for_backward(grad_x, g_all.data_t, g_all.inv_scale_t, xq.data_t, xq.inv_scale_t)
+        elif needs_grad:
+            ctx.save_for_backward(x, weight, targets)
+        if reduction == "mean":
+            return losses.sum() / num_valid  # ignored targets have loss 0
+        if reduction == "sum":
+            return losses.sum()
+        return losses
+
+    @staticmethod
+    def backward(ctx, g):
+        saved = ctx.saved_tensors
+        if not saved:
+            raise RuntimeError("softcap_cross_entropy: backward without grad mode in forward")
+        weight = ctx.weight
+        if ctx.precomputed:
+            grad_x, g_t, g_scale_t, x_t, x_scale_t = saved
+            gw = g.to(torch.float32).reshape(1)
+            if mx_grad_direct(weight):  # .grad (+)= g * dlogits^T . x, one GEMM
+                mx_grad_weights(g_t, g_scale_t, x_t, x_scale_t, [weight], gw)
+                return grad_x * g, None, None, None, None, None, None, None, None
+            dw = torch.empty(weight.shape, dtype=torch.float32, device=weight.device)
+            mx_gemm_f32(g_t, g_scale_t, x_t, x_scale_t, dw, False, gw)
+            return grad_x * g, dw.to(weight.dtype), None, None, None, None, None, None, None
+        x, weight, targets = saved
+        vocab, softcap, chunk_rows, cache = ctx.args
+        grad_x = torch.empty_like(x)
+        xq, g_all = _run_chunks(x, weight, targets, vocab, softcap, chunk_rows, None, grad_x,
+                                g.to(torch.float32).contiguous(), None, cache)
+        dw = torch.empty(weight.shape, dtype=torch.float32, device=weight.device)
+        mx_gemm_f32(g_all.data_t, g_all.inv_scale_t, xq.data_t, xq.inv_scale_t, dw, False)
+        return grad_x, dw.to(weight.dtype), None, None, None, None, None, None, None
+
+
+def softcap_cross_entropy(x: torch.Tensor, weight: torch.Tensor, targets: torch.Tensor, vocab_size: int,
+                          softcap: float, chunk_rows: int, reduction: str = "mean",
+                          cache: Optional[Fp8WeightCache] = None) -> torch.Tensor:
+    """lm_head + logit softcap + cross-entropy a chunk of rows at a time under the MX recipe, so that the full
+    (N, vocab) logits never exist (src/nanochat/model/ops/softcap_ce.h:16-24, recipe Mx). x: (N, C) bf16; weight:
+    (V_padded, C) fp32 lm_head weight; targets: (N) int64, -1 = ignored; logits are cropped to vocab_size and capped as
+    softcap * tanh(z / softcap); mean divides by the number of targets that are not ignored. MX needs N, C, chunk_rows
+    and V_padded % 128 (the reference falls back to other recipes otherwise, which are outside this library)."""
+    if x.dim() != 2 or targets.dim() != 1 or targets.size(0) != x.size(0):
+        raise ValueError("softcap_cross_entropy expects x (N, C) and targets (N)")
+    if chunk_rows < 1:
+        raise ValueError("chunk_rows must be positive")
+    if not x.is_cuda or x.dtype != torch.bfloat16:
+        raise ValueError("softcap_cross_entropy expects bf16 CUDA activations")
+    if reduction not in ("mean", "sum", "none"):
+        raise ValueError("reduction must be mean, sum or none")
+    if not (mx_fits(x.size(0), x.size(1)) and chunk_rows % 128 == 0 and weight.size(0) % 128 == 0
+            and weight.size(0) >= vocab_size and weight.size(1) == x.size(1)):
+        raise RuntimeError("softcap_cross_entropy: MX needs N, C, chunk_rows and the padded vocab % 128")
+    needs_grad = torch.is_grad_enabled() and (x.requires_grad or weight.requires_grad)
+    return _SoftcapCrossEntropy.apply(x.contiguous(), weight, targets.to(torch.int64).contiguous(), int(vocab_size),
+                                      float(softcap), int(chunk_rows), reduction, needs_grad, cache)

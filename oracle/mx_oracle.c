@@ -180,3 +180,72 @@ void mxo_residual_norm(const float* x, const float* r, const float* x0, float lr
       for (int c = 0; c < cols; ++c) n[row * cols + c] = mxo_round_bf16(res[row * cols + c] * rs);
   }
 }
+
+/* Loss pass of the chunked lm_head (src/nanochat/model/ops/softcap_ce_kernel.cu:62-103): per row of bf16 logits held as
+ * fp32, lse = softcap + log(sum exp(softcap * tanh(z / softcap) - softcap)) over the first `vocab` columns and
+ * loss = lse - capped[target]; target < 0: loss 0, lse untouched. Summed in the kernel's order (256 threads, thread t
+ * takes columns t * 8 + 2048 * i + k, a butterfly per warp, then a butterfly over the 8 warp sums) with the host's
+ * tanhf / expf / logf, which differ from the device's by a few ulp: this pins the structure, the tolerance is in the
+ * tests. loss and lse may be null. */
+void mxo_softcap_ce_loss(const float* logits, int64_t rows, int64_t ld, const int64_t* targets, int vocab, int padded,
+                         float softcap, float* loss, float* lse) {
+  for (int64_t row = 0; row < rows; ++row) {
+    const float* z = logits + row * ld;
+    const int64_t t = targets[row];
+    if (t < 0) {
+      if (loss) loss[row] = 0.f;
+      continue;
+    }
+    float part[256];
+    for (int th = 0; th < 256; ++th) {
+      float s = 0.f;
+      for (int j = th * 8; j < padded; j += 2048)
+        for (int k = 0; k < 8; ++k)
+          if (j + k < vocab) s += expf(softcap * tanhf(z[j + k] / softcap) - softcap);
+      part[th] = s;
+    }
+    float warp[32];
+    for (int w = 0; w < 32; ++w) warp[w] = 0.f;
+    for (int w = 0; w < 8; ++w) {
+      float lane[32];
+      for (int l = 0; l < 32; ++l) lane[l] = part[w * 32 + l];
+      for (int o = 16; o > 0; o >>= 1) {
+        float next[32];
+        for (int l = 0; l < 32; ++l) next[l] = lane[l] + lane[l ^ o];
+        memcpy(lane, next, sizeof(lane));
+      }
+      warp[w] = lane[0];
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+      float next[32];
+      for (int l = 0; l < 32; ++l) next[l] = warp[l] + warp[l ^ o];
+      memcpy(warp, next, sizeof(warp));
+    }
+    const float l = softcap + logf(warp[0]);
+    if (loss) loss[row] = l - softcap * tanhf(z[t] / softcap);
+    if (lse) lse[row] = l;
+  }
+}
+
+/* The gradient the quantizer's softcap prologue quantizes (softcap_ce_kernel.cu:49-54, 118-145), as bf16 values in
+ * fp32: g = bf16((p - onehot) * (1 - th * th) * scale), th = tanh(z / softcap), p = exp(softcap * th - lse[row]);
+ * scale = grad_scale ? grad_scale[row * stride] : 1, divided by num_valid when that is positive; rows with
+ * target < 0 and columns >= vocab give 0. */
+void mxo_softcap_ce_grad(const float* logits, int64_t rows, int64_t ld, const int64_t* targets, const float* lse,
+                         int vocab, int padded, float softcap, const float* grad_scale, int64_t stride,
+                         int64_t num_valid, float* g) {
+  for (int64_t row = 0; row < rows; ++row) {
+    const int64_t t = targets[row];
+    float scale = grad_scale ? grad_scale[row * stride] : 1.f;
+    if (num_valid > 0) scale /= (float)num_valid;
+    for (int c = 0; c < padded; ++c) {
+      float v = 0.f;
+      if (t >= 0 && c < vocab) {
+        const float th = tanhf(logits[row * ld + c] / softcap);
+        const float p = expf(softcap * th - lse[row]);
+        v = (p - (c == t ? 1.f : 0.f)) * (1.f - th * th) * scale;
+      }
+      g[row * padded + c] = mxo_round_bf16(v);
+    }
+  }
+}

@@ -275,6 +275,42 @@ def residual_norm(x, r=None, x0=None, lr: float = 1.0, l0: float = 0.0, eps: flo
     return s, res, rstd, n
 
 
+def softcap_ce_loss(logits, targets, vocab: int, softcap: float):
+    """Per row of bf16 logits held as fp32 (rows, padded): lse = log sum exp(capped) over the first `vocab` columns with
+    capped = softcap * tanh(z / softcap), loss = lse - capped[target]; target < 0: loss 0, lse nan (unset in the
+    kernel) (src/nanochat/model/ops/softcap_ce_kernel.cu:62-103). Computed in float64 and rounded: the kernel's fp32
+    tanhf / expf / logf and its summation order agree with this to a few ulp, not bit for bit."""
+    z = np.asarray(logits, dtype=np.float64)[:, :vocab]
+    t = np.asarray(targets, dtype=np.int64)
+    capped = softcap * np.tanh(z / softcap)
+    lse = np.log(np.exp(capped - softcap).sum(axis=1)) + softcap
+    rows = np.arange(z.shape[0])
+    loss = lse - capped[rows, np.clip(t, 0, vocab - 1)]
+    valid = t >= 0
+    return np.where(valid, loss, 0.0).astype(np.float32), np.where(valid, lse, np.nan).astype(np.float32)
+
+
+def softcap_ce_grad(logits, targets, lse, vocab: int, softcap: float, scale=1.0):
+    """The loss's gradient with respect to the logits as the bf16 the reference's grad kernel writes
+    (src/nanochat/model/ops/softcap_ce_kernel.cu:49-54, 105-114): bf16((p - onehot) * (1 - th^2) * scale) with
+    th = tanh(z / softcap), p = exp(softcap * th - lse); 0 for rows with target < 0 and for columns >= vocab. scale: a
+    number or one per row. In float64 then rounded: values that sit on a bf16 rounding boundary may differ from the
+    kernel's fp32 arithmetic by one bf16 ulp."""
+    z = np.asarray(logits, dtype=np.float64)
+    rows, padded = z.shape
+    t = np.asarray(targets, dtype=np.int64)
+    th = np.tanh(z / softcap)
+    lse64 = np.where(t >= 0, np.asarray(lse, dtype=np.float64), 0.0)
+    p = np.exp(softcap * th - lse64[:, None])
+    onehot = np.zeros_like(z)
+    valid = t >= 0
+    onehot[np.arange(rows)[valid], t[valid]] = 1.0
+    g = (p - onehot) * (1.0 - th * th) * (np.asarray(scale, dtype=np.float64).reshape(-1, 1) if np.ndim(scale) else scale)
+    g[:, vocab:] = 0.0
+    g[~valid] = 0.0
+    return round_bf16(g.astype(np.float32))
+
+
 def rel_norm_diff(a, b) -> float:
     """||a - b|| / ||b|| in fp64 (tests/test_fp8.cpp:20-23)."""
     a64, b64 = np.asarray(a, dtype=np.float64), np.asarray(b, dtype=np.float64)

@@ -1,6 +1,7 @@
-// C-callable door into the reference's own MX quantizer and fused residual-norm kernels, for parity pinning and
-// timing only. Compiled together with the unmodified reference sources (src/nanochat/model/fp8/fp8_kernel.cu and
-// src/nanochat/model/ops/residual_norm_kernel.cu, which pull in mx_kernel.cuh) taken from the reference tree at
+// C-callable door into the reference's own MX quantizer, fused residual-norm and softcap cross-entropy kernels, for
+// parity pinning and timing only. Compiled together with the unmodified reference sources
+// (src/nanochat/model/fp8/fp8_kernel.cu, src/nanochat/model/ops/residual_norm_kernel.cu and
+// src/nanochat/model/ops/softcap_ce_kernel.cu, which pull in mx_kernel.cuh) taken from the reference tree at
 // build time; nothing of them is copied here.
 // Test infrastructure: the product never loads this library.
 #include <cstdint>
@@ -9,6 +10,7 @@
 
 #include "nanochat/model/fp8/fp8_kernel.h"
 #include "nanochat/model/ops/residual_norm_kernel.h"
+#include "nanochat/model/ops/softcap_ce_kernel.h"
 
 extern "C" {
 
@@ -54,6 +56,27 @@ int ref_residual_norm_mx_fwd(const void* x, const void* r, const void* x0, const
                                                {data_t, ld_t, scale_t, scale_tiles_t},
                                                n_cols};
   nanochat::kernels::residual_norm_mx_fwd(a, static_cast<cudaStream_t>(stream));
+  return static_cast<int>(cudaGetLastError());
+}
+
+// nanochat::kernels::softcap_ce (src/nanochat/model/ops/softcap_ce_kernel.h:13-22). With grad != 0 the logits are
+// overwritten by their gradient.
+int ref_softcap_ce(void* logits, int64_t rows, int64_t ld, const int64_t* targets, int vocab, int padded, float softcap,
+                   float* loss, const float* grad_scale, int64_t grad_scale_stride, const int64_t* num_valid, int grad,
+                   float* lse, void* stream) {
+  nanochat::kernels::softcap_ce(logits, rows, ld, targets, vocab, padded, softcap, loss, grad_scale, grad_scale_stride,
+                                num_valid, grad != 0, nullptr, lse, static_cast<cudaStream_t>(stream));
+  return static_cast<int>(cudaGetLastError());
+}
+
+// nanochat::kernels::softcap_ce_grad_mx (src/nanochat/model/ops/softcap_ce_kernel.h:24-29)
+int ref_softcap_ce_grad_mx(const void* logits, int64_t rows, int64_t ld, const int64_t* targets, const float* lse,
+                           int vocab, int padded, float softcap, const float* grad_scale, int64_t grad_scale_stride,
+                           const int64_t* num_valid, void* data, int64_t ld_out, void* scale, int64_t scale_tiles,
+                           void* data_t, int64_t ld_t, void* scale_t, int64_t scale_tiles_t, void* stream) {
+  nanochat::kernels::softcap_ce_grad_mx(logits, rows, ld, targets, lse, vocab, padded, softcap, grad_scale,
+                                        grad_scale_stride, num_valid, {data, ld_out, scale, scale_tiles},
+                                        {data_t, ld_t, scale_t, scale_tiles_t}, static_cast<cudaStream_t>(stream));
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -52,5 +52,7 @@ def oracle_c():
     lib.mxo_quantize.argtypes = [vp, vp, i64, i64, i32, i32, i32, vp, i64, vp, i64]
     lib.mxo_dequantize.argtypes = [vp, vp, i64, i64, vp]
     lib.mxo_gemm_f32.argtypes = [vp, vp, vp, vp, vp, i64, i64, i64, ctypes.c_float, i32]
+    lib.mxo_softcap_ce_loss.argtypes = [vp, i64, i64, vp, i32, i32, ctypes.c_float, vp, vp]
+    lib.mxo_softcap_ce_grad.argtypes = [vp, i64, i64, vp, vp, i32, i32, ctypes.c_float, vp, i64, i64, vp]
     lib.mxo_residual_norm.argtypes = [vp, vp, vp, ctypes.c_float, ctypes.c_float, i64, i32, ctypes.c_float, vp, vp, vp, vp, vp]
     return lib

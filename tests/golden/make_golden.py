@@ -9,7 +9,10 @@ cuBLASLt's MXFP8 GEMM (torch._scaled_mm, the arithmetic of the reference's --gem
 src/nanochat/model/fp8/mx_gemm.cpp:158). residual_norm_*.npz: seeded inputs of the fused residual step and what the
 reference's own nanochat_residual_norm_mx_fwd_c* / nanochat_residual_norm_fwd_c* kernels
 (src/nanochat/model/ops/residual_norm_kernel.cu, compiled unmodified) wrote for them: s, res, rstd, the MX bytes of n in
-both layouts, and n itself from the plain kernel. The CPU test suite checks the oracle against these files.
+both layouts, and n itself from the plain kernel. softcap_ce_*.npz: bf16 logits, targets and per-row scales with what
+the reference's nanochat_softcap_ce_loss / nanochat_softcap_ce_loss_grad / nanochat_softcap_ce_grad_mx kernels
+(src/nanochat/model/ops/softcap_ce_kernel.cu, compiled unmodified) gave: loss, lse, the bf16 gradient and its MX bytes.
+The CPU test suite checks the oracle against these files.
 """
 import os
 import sys
@@ -76,6 +79,28 @@ def main():
         name = f"{R}x{C}" + ("_add" if add else "") + ("_blend" if blend else "")
         np.savez_compressed(os.path.join(out, f"residual_norm_{name}.npz"), **rec)
         print("wrote residual_norm", name)
+    for rows, padded, vocab, per_row in [(128, 256, 250, True), (128, 128, 128, False)]:
+        g = torch.Generator().manual_seed(31 + padded)
+        logits = (torch.randn(rows, padded, generator=g) * 8).to(torch.bfloat16)
+        targets = torch.randint(vocab, (rows,), generator=g, dtype=torch.int64)
+        targets[:5] = -1
+        grad_scale = torch.rand(rows, generator=g) + 0.5
+        z, t = logits.cuda(), targets.cuda()
+        scale = grad_scale.cuda() if per_row else None
+        valid = None if per_row else (t >= 0).sum()
+        loss, lse, _ = refkernel.softcap_ce(z, t, vocab, 15.0)
+        _, _, grad = refkernel.softcap_ce(z, t, vocab, 15.0, True, scale, valid)
+        mx = refkernel.softcap_ce_grad_mx(z, t, lse, vocab, 15.0, scale, valid)
+        torch.cuda.synchronize()
+        lse = torch.where(t >= 0, lse, torch.zeros_like(lse))  # unset for ignored rows
+        rec = {"logits_bf16_bits": bits(logits), "targets": targets.numpy(), "vocab": np.int32(vocab),
+               "softcap": np.float32(15.0), "loss": loss.cpu().numpy(), "lse": lse.cpu().numpy(),
+               "grad_bf16_bits": bits(grad.cpu()), "num_valid": np.int64(0 if per_row else int(valid.item()))}
+        if per_row:
+            rec["grad_scale"] = grad_scale.numpy()
+        rec.update({k: v.cpu().numpy() for k, v in zip(("data", "scale", "data_t", "scale_t"), mx)})
+        np.savez_compressed(os.path.join(out, f"softcap_ce_{rows}x{padded}.npz"), **rec)
+        print("wrote softcap_ce", rows, padded)
     for M, N, K in [(128, 128, 128), (256, 384, 512)]:
         a, b = gemm_operands(M, N, K)
         qa = refkernel.quantize_mx(a.cuda())

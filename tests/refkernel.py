@@ -89,3 +89,50 @@ def residual_norm(x, r=None, x0=None, lr=None, l0=None, layer=0, gate_cols=0, mx
         err = l.ref_residual_norm_fwd(*base, stream)
     assert err == 0, f"reference kernel launch failed: {err}"
     return out
+
+
+def _bind_softcap(l):
+    vp, i64, i32, f32 = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int, ctypes.c_float
+    l.ref_softcap_ce.argtypes = [vp, i64, i64, vp, i32, i32, f32, vp, vp, i64, vp, i32, vp, vp]
+    l.ref_softcap_ce_grad_mx.argtypes = [vp, i64, i64, vp, vp, i32, i32, f32, vp, i64, vp, vp, i64, vp, i64, vp, i64, vp,
+                                         i64, vp]
+
+
+def softcap_ce(logits, targets, vocab, softcap, grad=False, grad_scale=None, num_valid=None):
+    """Runs nanochat::kernels::softcap_ce on a copy of the logits. Returns (loss, lse, grad): grad is the bf16 gradient
+    the kernel wrote over the logits when grad is set, else None."""
+    l = lib()
+    if not hasattr(l, "_ce_bound"):
+        _bind_softcap(l)
+        l._ce_bound = True
+    z = logits.clone()
+    rows, padded = z.shape
+    loss = torch.zeros(rows, dtype=torch.float32, device=z.device)
+    lse = torch.zeros(rows, dtype=torch.float32, device=z.device)
+    err = l.ref_softcap_ce(z.data_ptr(), rows, padded, targets.data_ptr(), vocab, padded, softcap, loss.data_ptr(),
+                           grad_scale.data_ptr() if grad_scale is not None else None, 1,
+                           num_valid.data_ptr() if num_valid is not None else None, int(grad), lse.data_ptr(),
+                           torch.cuda.current_stream().cuda_stream)
+    assert err == 0, f"reference kernel launch failed: {err}"
+    return loss, lse, (z if grad else None)
+
+
+def softcap_ce_grad_mx(logits, targets, lse, vocab, softcap, grad_scale=None, num_valid=None):
+    """Runs nanochat::kernels::softcap_ce_grad_mx. Returns (data, scale, data_t, scale_t)."""
+    l = lib()
+    if not hasattr(l, "_ce_bound"):
+        _bind_softcap(l)
+        l._ce_bound = True
+    R, C = logits.shape
+    dev = logits.device
+    data = torch.zeros((R, C), dtype=torch.uint8, device=dev)
+    data_t = torch.zeros((C, R), dtype=torch.uint8, device=dev)
+    scale = torch.zeros(R * C // 32, dtype=torch.uint8, device=dev)
+    scale_t = torch.zeros(R * C // 32, dtype=torch.uint8, device=dev)
+    err = l.ref_softcap_ce_grad_mx(logits.data_ptr(), R, C, targets.data_ptr(), lse.data_ptr(), vocab, C, softcap,
+                                   grad_scale.data_ptr() if grad_scale is not None else None, 1,
+                                   num_valid.data_ptr() if num_valid is not None else None, data.data_ptr(), C,
+                                   scale.data_ptr(), C // 128, data_t.data_ptr(), R, scale_t.data_ptr(), R // 128,
+                                   torch.cuda.current_stream().cuda_stream)
+    assert err == 0, f"reference kernel launch failed: {err}"
+    return data, scale, data_t, scale_t

@@ -23,7 +23,9 @@ int main() {
   const char* (*gr)(const void*, const void*, const void*, const void*, void*, void*, void*, void*, void*, int64_t, int64_t, int64_t, cudaStream_t) = &k::b200_mx_gemm_relu_square;
   const char* (*grb)(const void*, const void*, const void*, const void*, const void*, void*, void*, void*, void*, int64_t, int64_t, int64_t, cudaStream_t) = &k::b200_mx_gemm_relu_square_bwd;
   void (*rn)(const k::ResidualNormMxFwd&, cudaStream_t) = &k::residual_norm_mx_fwd;
-  (void)q; (void)qb; (void)g16; (void)g32; (void)gr; (void)grb; (void)rn;
+  void (*ce)(void*, int64_t, int64_t, const int64_t*, int, int, float, float*, const float*, int64_t, const int64_t*, bool, float*, float*, cudaStream_t) = &k::softcap_ce;
+  void (*cg)(const void*, int64_t, int64_t, const int64_t*, const float*, int, int, float, const float*, int64_t, const int64_t*, k::MxOut, k::MxOut, cudaStream_t) = &k::softcap_ce_grad_mx;
+  (void)q; (void)qb; (void)g16; (void)g32; (void)gr; (void)grb; (void)rn; (void)ce; (void)cg;
   k::ResidualNormMxFwd norm{};
   norm.base.rows = 128, norm.base.cols = 128;
   k::residual_norm_mx_fwd(norm, nullptr);

@@ -219,3 +219,72 @@ def test_residual_norm_oracle_matches_reference_kernel_golden(path):
     want = mo.quantize_mx(n)
     for key in ("data", "scale", "data_t", "scale_t"):
         assert np.array_equal(want[key].reshape(-1), g[key].reshape(-1)), (os.path.basename(path), key)
+
+
+# ---------------------------------------------------------------- chunked lm_head loss
+
+def _ce_case(rows=128, padded=256, vocab=250, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    logits = (torch.randn(rows, padded, generator=g) * 8).to(torch.bfloat16)
+    targets = torch.randint(vocab, (rows,), generator=g, dtype=torch.int64)
+    targets[:5] = -1
+    scale = torch.rand(rows, generator=g) + 0.5
+    return np.ascontiguousarray(np_f32(logits)), targets.numpy(), scale.numpy(), vocab
+
+
+def test_softcap_ce_oracles_agree_and_match_torch(oracle_c):
+    """numpy (float64) and C (fp32 in the kernel's summation order) restatements against each other and against
+    torch's cross_entropy of the capped logits (tests/test_softcap_ce.cpp:27-35)."""
+    z, t, scale, vocab = _ce_case()
+    rows, padded = z.shape
+    loss, lse = mo.softcap_ce_loss(z, t, vocab, 15.0)
+    closs, clse = np.zeros(rows, np.float32), np.zeros(rows, np.float32)
+    oracle_c.mxo_softcap_ce_loss(z.ctypes.data, rows, padded, t.ctypes.data, vocab, padded, 15.0, closs.ctypes.data,
+                                 clse.ctypes.data)
+    valid = t >= 0
+    assert np.allclose(loss, closs, rtol=2e-6, atol=2e-6) and np.allclose(lse[valid], clse[valid], rtol=1e-6)
+    capped = 15 * torch.tanh(torch.from_numpy(z[:, :vocab]) / 15)
+    want = torch.nn.functional.cross_entropy(capped, torch.from_numpy(t), ignore_index=-1, reduction="none").numpy()
+    assert np.allclose(loss, want, rtol=1e-5, atol=1e-5)
+    # gradient: autograd of the same graph, scaled per row
+    zt = torch.from_numpy(z).double().requires_grad_()
+    l = torch.nn.functional.cross_entropy(15 * torch.tanh(zt[:, :vocab] / 15), torch.from_numpy(t), ignore_index=-1,
+                                          reduction="none")
+    (l * torch.from_numpy(scale).double()).sum().backward()
+    g = mo.softcap_ce_grad(z, t, lse, vocab, 15.0, scale)
+    assert np.abs(g - zt.grad.numpy()).max() <= 2.0 ** -8 * np.abs(zt.grad.numpy()).max()
+    cg = np.zeros_like(z)
+    oracle_c.mxo_softcap_ce_grad(z.ctypes.data, rows, padded, t.ctypes.data, clse.ctypes.data, vocab, padded, 15.0,
+                                 np.ascontiguousarray(scale).ctypes.data, 1, 0, cg.ctypes.data)
+    assert (cg != g).mean() < 2e-3 and np.abs(cg - g).max() <= 2.0 ** -7 * np.abs(g).max()
+
+
+def _ce_golden_files():
+    return sorted(glob.glob(os.path.join(GOLDEN, "softcap_ce_*.npz")))
+
+
+@pytest.mark.parametrize("path", _ce_golden_files() or [None])
+def test_softcap_ce_oracle_matches_reference_kernel_golden(path):
+    """What the reference's own softcap cross-entropy kernels gave on a B200 (tests/golden/make_golden.py): loss and
+    lse to fp32 rounding (host and device tanh / exp / log differ in the last bits), the bf16 gradient and its MX
+    bytes up to the rare value that sits on a rounding boundary; quantize_mx of the kernel's own bf16 gradient bit for
+    bit."""
+    if path is None:
+        pytest.skip("no golden files yet")
+    g = np.load(path)
+    z = mo.bf16_bits_to_f32(g["logits_bf16_bits"])
+    t, vocab, softcap = g["targets"], int(g["vocab"]), float(g["softcap"])
+    valid = t >= 0
+    loss, lse = mo.softcap_ce_loss(z, t, vocab, softcap)
+    assert np.allclose(loss, g["loss"], rtol=2e-6, atol=2e-6)
+    assert np.allclose(lse[valid], g["lse"][valid], rtol=1e-6)
+    scale = g["grad_scale"] if "grad_scale" in g else 1.0
+    if int(g["num_valid"]) > 0:
+        scale = scale / np.float32(int(g["num_valid"]))
+    grad = mo.softcap_ce_grad(z, t, g["lse"], vocab, softcap, scale)
+    want_grad = mo.bf16_bits_to_f32(g["grad_bf16_bits"])
+    assert (grad != want_grad).mean() < 2e-3
+    assert np.abs(grad - want_grad).max() <= 2.0 ** -7 * np.abs(want_grad).max()
+    q = mo.quantize_mx(want_grad)
+    for key in ("data", "scale", "data_t", "scale_t"):
+        assert np.array_equal(q[key].reshape(-1), g[key].reshape(-1)), (os.path.basename(path), key)
