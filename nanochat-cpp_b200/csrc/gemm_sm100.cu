@@ -47,13 +47,7 @@ static __device__ __align__(256) unsigned char g_static_splitk_scratch[MXB200_ST
 __device__ unsigned long long g_trace[8192];
 #define TRACE(slot, idx) \
   do { if (blockIdx.x == 0 && (idx) < 64) g_trace[(slot) * 64 + (idx)] = clock64(); } while (0)
-__device__ int g_exp;  // experiment switch of the tracing build
-__device__ int g_chunk_calls;
-#define STAMP(k) do { if (stamp) g_trace[5 * 64 + (k)] = clock64(); } while (0)
-#define EXP(bit) ((g_exp >> (bit)) & 1)
 #else
-#define EXP(bit) 0
-#define STAMP(k) do { } while (0)
 #define TRACE(slot, idx) do { } while (0)
 #endif
 
@@ -692,12 +686,6 @@ __device__ __forceinline__ void fused_quantize_chunk(const GemmParams& p, const 
   // The previous chunk's TMA stores may still be reading st_out / st_q / st_qt: everything up to the point where those
   // are written again (all of the arithmetic) runs first, and only then does the warp wait for the reads to finish.
 
-#ifdef MXB200_TRACE
-  bool stamp = false;
-  if (blockIdx.x == 0 && threadIdx.x == 64)
-    stamp = (g_chunk_calls++ == 21);
-#endif
-  STAMP(0);
   // ---- the values to quantize: this thread's row of the block, 32 bf16 as 16 packed words
   uint32_t v[16];
   uint32_t o[kFuse == kFuseReluSquare ? 16 : 1];
@@ -737,7 +725,6 @@ __device__ __forceinline__ void fused_quantize_chunk(const GemmParams& p, const 
     }
   }
 
-  STAMP(1);
   // ---- columns, first half: into the transpose tile, 64 bytes per column (its 32 rows as bf16). A store instruction
   // puts one column's 32 rows there (32 lanes x 2 bytes, conflict-free); the 16-byte pieces of column c sit at piece
   // index xor (c >> 1) & 3, so that lane c then reads its column as four 16-byte vectors without bank conflicts.
@@ -752,19 +739,12 @@ __device__ __forceinline__ void fused_quantize_chunk(const GemmParams& p, const 
       *reinterpret_cast<uint16_t*>(mine[k & 3] + (2 * k + 1) * 64) = static_cast<uint16_t>(v[k] >> 16);
     }
   }
-  STAMP(2);
   __syncwarp();
-  STAMP(3);
 
   // ---- rows: this thread's 32 values are one block
   uint32_t wq[8];
-  int e_row = 0;
-  if (!EXP(1))
-    e_row = quantize_block(v, p.floor_rule, wq);
-  else
-    for (int k = 0; k < 8; ++k) wq[k] = v[k];
+  const int e_row = quantize_block(v, p.floor_rule, wq);
 
-  STAMP(4);
   // ---- columns, second half: lane c owns column c
   uint32_t wqt[8];
   int e_col;
@@ -775,32 +755,24 @@ __device__ __forceinline__ void fused_quantize_chunk(const GemmParams& p, const 
       const uint4 t = *reinterpret_cast<const uint4*>(st_tr + lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4));
       c[4 * j] = t.x, c[4 * j + 1] = t.y, c[4 * j + 2] = t.z, c[4 * j + 3] = t.w;
     }
-    if (!EXP(2))
-      e_col = quantize_block(c, p.floor_rule, wqt);
-    else {
-      e_col = 0;
-      for (int k = 0; k < 8; ++k) wqt[k] = c[k];
-    }
+    e_col = quantize_block(c, p.floor_rule, wqt);
   }
 
-  STAMP(5);
   // ---- results out: scale bytes straight to their swizzled positions, data through the staging tiles
-  if (valid && !EXP(4)) {
+  if (valid) {
     const int b = col >> 5;
     p.q_scale[(static_cast<int64_t>(row >> 7) * p.q_scale_tiles + (b >> 2)) * kScaleTileBytes +
               mx_scale_tile_offset(static_cast<int>(row & 127), b)] = static_cast<uint8_t>(e_row);
   }
   const int n = col + lane;  // row of the transposed layout
-  if (warp_row0 < p.M && n < p.N && !EXP(4)) {
+  if (warp_row0 < p.M && n < p.N) {
     const int b = warp_row0 >> 5;
     p.qt_scale[(static_cast<int64_t>(n >> 7) * p.qt_scale_tiles + (b >> 2)) * kScaleTileBytes +
                mx_scale_tile_offset(n & 127, b)] = static_cast<uint8_t>(e_col);
   }
-  STAMP(6);
   if (lane == 0)
     tma_store_wait_read<0>();  // the previous chunk's stores have been read out of the staging tiles
   __syncwarp();
-  STAMP(7);
   if constexpr (kFuse == kFuseReluSquare) {
 #pragma unroll
     for (int j = 0; j < 4; ++j)  // h itself leaves as the plain epilogue's output does
@@ -809,18 +781,15 @@ __device__ __forceinline__ void fused_quantize_chunk(const GemmParams& p, const 
   }
   park_block(wq, st_q, lane);
   park_block(wqt, st_qt, lane);
-  STAMP(8);
   fence_proxy_async_smem();
   __syncwarp();
-  STAMP(9);
-  if (lane == 0 && warp_row0 < p.M && col < p.N && !EXP(3)) {
+  if (lane == 0 && warp_row0 < p.M && col < p.N) {
     if constexpr (kFuse == kFuseReluSquare)
       tma_store_2d(map_d, st_out, col, warp_row0);
     tma_store_2d(map_q, st_q, col, warp_row0);
     tma_store_2d(map_qt, st_qt, warp_row0, col);
     tma_store_commit();
   }
-  STAMP(10);
 }
 
 // ------------------------------------------------------------------------------------------------ CTA-pair kernel
@@ -1621,11 +1590,6 @@ extern "C" int mxb200_gemm_splitk_static(const void* a, const void* a_scale, con
 }
 
 #ifdef MXB200_TRACE
-extern "C" __attribute__((visibility("default"))) int mxb200_trace_set(int v) {
-  const int zero = 0;
-  cudaMemcpyToSymbol(mxb200::g_chunk_calls, &zero, sizeof(zero));
-  return cudaMemcpyToSymbol(mxb200::g_exp, &v, sizeof(v)) == cudaSuccess ? 0 : 1;
-}
 extern "C" __attribute__((visibility("default"))) int mxb200_trace_read(unsigned long long* out, int n) {
   cudaDeviceSynchronize();
   return cudaMemcpyFromSymbol(out, mxb200::g_trace, sizeof(unsigned long long) * n) == cudaSuccess ? 0 : 1;
