@@ -678,7 +678,7 @@ template <int kFuse>
 __device__ __forceinline__ void fused_quantize_chunk(const GemmParams& p, const CUtensorMap* map_d,
                                                      const CUtensorMap* map_q, const CUtensorMap* map_qt,
                                                      unsigned char* stage, int lane, const float* acc, int64_t row,
-                                                     int col, int warp_row0, bool valid, const uint4* h_pieces) {
+                                                     int col, int warp_row0, bool valid, uint4* h_pieces, int next_col) {
   unsigned char* st_out = stage;         // TMA source (forward form); h hand-over buffer (backward form, never a source)
   unsigned char* st_tr = stage + 2048;   // transpose tile, only ever touched by this warp's threads
   unsigned char* st_q = stage + 4096;    // TMA source
@@ -698,7 +698,8 @@ __device__ __forceinline__ void fused_quantize_chunk(const GemmParams& p, const 
     }
   } else {
     // h's 32 x 32 block was loaded coalesced (load_h_pieces: 4 lanes per 64-byte row segment, 8 rows per
-    // instruction, issued a chunk ahead) and is handed to the row owners through the otherwise unused output buffer
+    // instruction, issued a chunk ahead) and is handed to the row owners through the otherwise unused output buffer;
+    // the pieces' registers then take the next chunk's block (next_col >= 0), which has this whole chunk to arrive
     uint32_t hw[16];
     if (warp_row0 < p.M && col < p.N) {
 #pragma unroll
@@ -718,6 +719,8 @@ __device__ __forceinline__ void fused_quantize_chunk(const GemmParams& p, const 
       for (int k = 0; k < 16; ++k)
         hw[k] = 0;
     }
+    if (next_col >= 0)
+      load_h_pieces(p, lane, warp_row0, next_col, h_pieces);
 #pragma unroll
     for (int k = 0; k < 16; ++k) {  // dh = bf16(h <= 0 ? 0 : bf16(ga) * 2h)
       const uint32_t g = pack_bf16x2_rn(acc[2 * k], acc[2 * k + 1]);
@@ -814,13 +817,20 @@ __device__ __forceinline__ void fused_quantize_chunk(const GemmParams& p, const 
 constexpr int kEpiStageBytes = 2048;       // one epilogue warp's staging buffer for TMA stores
 constexpr int kEpiFusedBytes = 6144;       // ... with a fused quantizer: output rows, transpose tile, q rows, q_t rows
 
-constexpr int kPairThreads = 320;          // producer warp, MMA warp, 8 epilogue warps
-constexpr int kPairEpilogueThreads = 256;  // two warps per TMEM lane quarter, each half of the tile's columns
+// Threads: producer warp, MMA warp, then the epilogue warps, kParts per TMEM lane quarter, each taking a share of the
+// tile's 32-column chunks. The plain epilogue keeps up with the main loop with two per quarter. The fused quantizers
+// execute several hundred instructions per chunk and thread and are bound by instruction latency, not by a pipe: a
+// third warp per quarter fills the idle issue slots (128 registers per thread hold both forms without spills worth
+// the name; a fourth would leave under 100).
 
 template <int TN, int kFuse = kFuseNone>
 struct PairConfig {
   static_assert(TN == 192 || TN == 256, "tile width");
   static constexpr int kEpiBytes = kFuse == kFuseNone ? kEpiStageBytes : kEpiFusedBytes;
+  static constexpr int kParts = kFuse == kFuseNone ? 2 : 3;
+  static constexpr int kEpiWarps = 4 * kParts;
+  static constexpr int kEpiThreads = 32 * kEpiWarps;
+  static constexpr int kThreads = 64 + kEpiThreads;
   static constexpr int kTileM = 256, kTileN = TN;
   static constexpr int kBRows = TN / 2;                // this CTA's rows of B
   static constexpr int kSfbTiles = 2;
@@ -828,16 +838,17 @@ struct PairConfig {
   static constexpr uint32_t kBBytes = kBRows * kBK;
   static constexpr uint32_t kSfBytes = kScaleTileBytes * (1 + kSfbTiles);  // A: own 128 rows; B: all its tiles
   static constexpr uint32_t kTxPerCta = kABytes + kBBytes + kSfBytes;
-  static constexpr int kStages = (TN == 192 ? 7 : 6) - (kFuse == kFuseNone ? 0 : 1);
+  static constexpr int kStages = (TN == 192 ? 7 : 6) - (kFuse == kFuseNone ? 0 : 2);
   static constexpr bool kOverlap = TN == 256;
   static constexpr uint32_t kAcc0 = 0, kAcc1 = kOverlap ? 224 : TN;
   static constexpr uint32_t kSfaCol = kOverlap ? 480 : 2 * TN, kSfbCol = kSfaCol + 4;
   static constexpr size_t kSmemBytes = 1024 + static_cast<size_t>(kStages) * (kABytes + kBBytes + kSfBytes) +
-                                       kPairEpilogueThreads / 32 * kEpiBytes + 256;
+                                       kEpiWarps * kEpiBytes + 256;
+  static_assert(kSmemBytes <= 232448, "shared memory per CTA");
 };
 
 template <int TN, int kFuse>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairConfig<TN, kFuse>::kThreads, 1)
       mxb200_mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                                  const __grid_constant__ CUtensorMap map_sfa,
                                  const __grid_constant__ CUtensorMap map_sfb,
@@ -851,7 +862,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
   unsigned char* s_a = smem;
   unsigned char* s_b = s_a + C::kStages * C::kABytes;
   unsigned char* s_epi = s_b + C::kStages * C::kBBytes;  // 2 KB per epilogue warp: 32 rows x 64 bytes
-  unsigned char* s_sf = s_epi + kPairEpilogueThreads / 32 * C::kEpiBytes;  // per stage: A's tile, B's two tiles
+  unsigned char* s_sf = s_epi + C::kEpiWarps * C::kEpiBytes;  // per stage: A's tile, B's two tiles
   Barriers* bars = reinterpret_cast<Barriers*>(s_sf + C::kStages * C::kSfBytes);
 
   const int warp = static_cast<int>(threadIdx.x) >> 5, lane = static_cast<int>(threadIdx.x) & 31;
@@ -867,10 +878,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&bars->tmem_full[a], 1);
-      mbar_init(&bars->tmem_empty[a], 16);  // one arrival per epilogue warp of either CTA (leader's copy is used)
+      mbar_init(&bars->tmem_empty[a], 2 * C::kEpiWarps);  // one arrival per epilogue warp of either CTA (leader's copy is used)
     }
     mbar_init(&bars->overlap_free, 8);  // the four warps per CTA that own the shared columns
-    mbar_init(&bars->epi_sync, kPairEpilogueThreads);
+    mbar_init(&bars->epi_sync, C::kEpiThreads);
     bars->abort_flag = 0;
     bars->last_flag = 0;
     fence_mbar_init();
@@ -1004,20 +1015,23 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
       }
     }
   } else {
-    // ------------------------------------------------------------------ epilogue (warps 2..9, both CTAs)
-    // A warp may read only the TMEM lanes of its quarter (warp id % 4); two warps share each quarter and take
-    // one half of the tile's columns each. TMEM loads are software-pipelined: the next 32 columns are in flight
-    // while the current 32 are converted and stored.
+    // ------------------------------------------------------------------ epilogue (warps 2 and up, both CTAs)
+    // A warp may read only the TMEM lanes of its quarter (warp id % 4); kParts warps share each quarter and take
+    // a contiguous share of the tile's 32-column chunks each. TMEM loads are software-pipelined: the next 32
+    // columns are in flight while the current 32 are converted and stored.
     const int quarter = warp & 3;
-    const int col_half = (warp - 2) >> 2;
+    const int col_part = (warp - 2) >> 2;
     const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
     const float alpha = (p.out_kind == kOutF32 && p.alpha != nullptr) ? *p.alpha : 1.f;
     uint32_t local = 0, sync_phase = 0;
     bool ok = true;
     constexpr int kChunks = C::kTileN / 32;
-    constexpr int kMine = (kChunks + 1) / 2;  // chunks of column half 0; half 1 takes the remaining kChunks - kMine
-    constexpr int kHalf = 128 * C::kTileN;    // elements of one CTA's half tile
-    const int n_mine = col_half == 0 ? kMine : kChunks - kMine;
+    constexpr int kMine = (kChunks + C::kParts - 1) / C::kParts;  // the most chunks any part takes
+    constexpr int kHalf = 128 * C::kTileN;                        // elements of one CTA's half tile
+    // part p takes chunks [first, first + n_mine): the remainder of kChunks / kParts goes to the leading parts
+    const int n_mine = kChunks / C::kParts + (col_part < kChunks % C::kParts ? 1 : 0);
+    const int first = col_part * (kChunks / C::kParts) + min(col_part, kChunks % C::kParts);
+    constexpr int kLast = C::kParts - 1;
     const uint32_t empty_leader[2] = {map_to_cta(smem_u32(&bars->tmem_empty[0]), 0),
                                       map_to_cta(smem_u32(&bars->tmem_empty[1]), 0)};
     const uint32_t overlap_leader = map_to_cta(smem_u32(&bars->overlap_free), 0);
@@ -1026,11 +1040,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
       const TileCoord tc = decode_unit(p, unit);
       const uint32_t buf = local & 1u, use = local >> 1;
       // the relu^2 backward form reads h: the first chunk's block is requested before the accumulator is waited for
-      uint4 h_pieces[2][4];
+      uint4 h_pieces[4];
       if constexpr (kFuse == kFuseReluSquareBwd) {
-        const int c0 = (C::kOverlap && buf == 0 && col_half == 1) ? kChunks - 1 : col_half * kMine;
+        const int c0 = (C::kOverlap && buf == 0 && col_part == kLast) ? kChunks - 1 : first;
         load_h_pieces(p, lane, tc.m * C::kTileM + static_cast<int>(rank) * 128 + quarter * 32, tc.n * C::kTileN + c0 * 32,
-                      h_pieces[0]);
+                      h_pieces);
       }
       if (!wait_bounded(&bars->tmem_full[buf], use & 1u, bars, kSiteEpilogueFull)) {
         ok = false;
@@ -1046,13 +1060,13 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
       const int64_t half_index = (static_cast<int64_t>(tc.tile) * p.splits + tc.split) * 2 + rank;
       float* part = p.splits > 1 ? p.partials + half_index * kHalf + static_cast<int64_t>(quarter * 32 + lane) * C::kTileN
                                  : nullptr;
-      // Overlapping buffers: buffer 0 shares its last 32 columns (owned by column half 1), buffer 1 its first 32
-      // (column half 0). The owning warps read those first and hand them over before anything else.
-      const bool owns_shared = C::kOverlap && ((buf == 0) == (col_half == 1));
+      // Overlapping buffers: buffer 0 shares its last 32 columns (owned by the last part), buffer 1 its first 32
+      // (part 0). The owning warps read those first and hand them over before anything else.
+      const bool owns_shared = C::kOverlap && (buf == 0 ? col_part == kLast : col_part == 0);
       auto chunk_of = [&](int i) {
-        if (C::kOverlap && buf == 0 && col_half == 1)
-          return i == 0 ? kChunks - 1 : kMine + i - 1;
-        return col_half * kMine + i;
+        if (C::kOverlap && buf == 0 && col_part == kLast)
+          return i == 0 ? kChunks - 1 : first + i - 1;
+        return first + i;
       };
       uint32_t r[2][32];
       tmem_ld_32x32b_x32(acc_t + chunk_of(0) * 32, r[0]);
@@ -1064,8 +1078,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
         tmem_ld_wait();
         if (i + 1 < n_mine) {
           tmem_ld_32x32b_x32(acc_t + chunk_of(i + 1) * 32, r[(i + 1) & 1]);
-          if constexpr (kFuse == kFuseReluSquareBwd)
-            load_h_pieces(p, lane, warp_row0, col0 + chunk_of(i + 1) * 32, h_pieces[(i + 1) & 1]);
         }
         if (i == 0 && owns_shared) {
           tcgen05_fence_before_sync();
@@ -1081,7 +1093,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
           store_rows_tma(&map_part, stage, lane, r[i & 1] + 16, c * 32 + 16, part_row0, true);
         } else if constexpr (kFuse != kFuseNone) {
           fused_quantize_chunk<kFuse>(p, &map_d, &map_q, &map_qt, stage, lane, reinterpret_cast<const float*>(r[i & 1]),
-                                      row, col, warp_row0, row_ok && col < p.N, h_pieces[i & 1]);
+                                      row, col, warp_row0, row_ok && col < p.N, h_pieces,
+                                      i + 1 < n_mine ? col0 + chunk_of(i + 1) * 32 : -1);
         } else {
           const bool valid = row_ok && col < p.N;
           const bool issue = warp_row0 < p.M && col < p.N;
@@ -1134,7 +1147,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
           const int sub = lane * 8;
           if (sub < C::kTileN && col0 + sub < p.N) {
 #pragma unroll 1
-            for (int rr = warp - 2; rr < 128; rr += kPairEpilogueThreads / 32) {
+            for (int rr = warp - 2; rr < 128; rr += C::kEpiWarps) {
               const int64_t grow = static_cast<int64_t>(tc.m) * C::kTileM + rank * 128 + rr;
               if (grow >= p.M)
                 break;
@@ -1328,8 +1341,8 @@ int launch_pair(const PairMaps& m, const GemmParams& p, int pairs, cudaStream_t 
   static bool configured[64] = {};
   if (int st = set_smem_once(mxb200_mx_gemm_pair_kernel<TN, kFuse>, C::kSmemBytes, configured); st != MXB200_OK)
     return st;
-  mxb200_mx_gemm_pair_kernel<TN, kFuse><<<2 * pairs, kPairThreads, C::kSmemBytes, stream>>>(m.a, m.b, m.sfa, m.sfb, m.d,
-                                                                                           m.part, m.q, m.qt, p);
+  mxb200_mx_gemm_pair_kernel<TN, kFuse><<<2 * pairs, C::kThreads, C::kSmemBytes, stream>>>(m.a, m.b, m.sfa, m.sfb, m.d,
+                                                                                          m.part, m.q, m.qt, p);
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return launch_status();
 }
