@@ -76,6 +76,14 @@ __device__ __forceinline__ uint32_t max_abs_u16x2(uint32_t m, uint32_t w) {
   return d;
 }
 
+// Running maximum of |x| over packed bf16 that skips NaN as fmaxf does (a NaN operand returns the other one), one
+// instruction per word. The result's sign bits carry no meaning (xor of the operands' signs): mask them off at the end.
+__device__ __forceinline__ uint32_t max_abs_skip_nan_bf16x2(uint32_t m, uint32_t w) {
+  uint32_t d;
+  asm("max.xorsign.abs.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(m), "r"(w));
+  return d;
+}
+
 // The block maximum as the quantizer defines it (fmaxf over |x|, which skips NaN) from the packed running maximum m
 // of `count` words: the fast path when no NaN was seen, else a second pass with fmaxf.
 __device__ __forceinline__ float amax_from_packed(uint32_t m, const uint32_t* words, int count) {

@@ -654,11 +654,12 @@ __device__ __forceinline__ void load_h_pieces(const GemmParams& p, int lane, int
 // Quantizes one scale block held as 16 packed words (32 bf16 in block order) into 32 e4m3 bytes w[8]; returns the
 // block's biased exponent.
 __device__ __forceinline__ int quantize_block(const uint32_t* v, int floor_rule, uint32_t* w) {
-  uint32_t m = 0u;
+  uint32_t m = 0u;  // NaN operands are skipped, as by the quantizer's fmaxf
 #pragma unroll
   for (int k = 0; k < 16; ++k)
-    m = max_abs_u16x2(m, v[k]);
-  const int e = mx_exponent(__float_as_uint(amax_from_packed(m, v, 16)), floor_rule);
+    m = max_abs_skip_nan_bf16x2(m, v[k]);
+  m &= 0x7fff7fffu;
+  const int e = mx_exponent(max(m & 0xffffu, m >> 16) << 16, floor_rule);
   const uint32_t mul2 = (mx_multiplier_bits(e) >> 16) * 0x10001u;
 #pragma unroll
   for (int k = 0; k < 8; ++k)

@@ -5,7 +5,7 @@
 // One CTA owns a 128 x 128 tile, which is exactly one 512-byte swizzled scale tile in each layout.
 //   row pass:    each thread loads 16 consecutive values with 256-bit loads (one for bf16, two for fp32), fully
 //                coalesced; the block maximum of 32 values is a 2-lane shuffle (for plain bf16 input the
-//                per-thread maximum is taken on the packed 16-bit patterns); 16 E4M3 bytes leave with one
+//                per-thread maximum and the multiply by the power-of-two scale stay packed bf16x2); 16 E4M3 bytes leave with one
 //                128-bit store (a warp writes 512 contiguous bytes). The loaded values are parked in shared
 //                memory in their input type (prologue values are bf16-exact).
 //   column pass: each thread owns two adjacent columns x 32 rows, read from shared memory as packed pairs
@@ -16,6 +16,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp8.h>
 
+#include "bf16x2_sm100.cuh"
 #include "internal.h"
 #include "mx_common.cuh"
 
@@ -106,21 +107,6 @@ __device__ __forceinline__ uint32_t cvt_e4m3x4(float a, float b, float c, float 
   return cvt_e4m3x2(a, b) | (cvt_e4m3x2(c, d) << 16);
 }
 
-__device__ __forceinline__ uint32_t max_u16x2(uint32_t a, uint32_t b) {
-  uint32_t r;
-  asm("max.u16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
-  return r;
-}
-
-// bits of max |x| over 16 bf16 values (8 packed words), NaNs included as the largest patterns
-__device__ __forceinline__ uint32_t absmax_bits_bf16x16(const uint32_t (&w)[8]) {
-  uint32_t m = max_u16x2(w[0] & 0x7fff7fffu, w[1] & 0x7fff7fffu);
-#pragma unroll
-  for (int k = 2; k < 8; ++k)
-    m = max_u16x2(m, w[k] & 0x7fff7fffu);
-  return max(m & 0xffffu, m >> 16);
-}
-
 __device__ __forceinline__ void load_u32x8_stream(const void* p, uint32_t (&w)[8], bool wide) {
   if (wide) {
     asm volatile("ld.global.nc.L1::no_allocate.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
@@ -192,22 +178,21 @@ __global__ void __launch_bounds__(kThreads, (kIn32 || kPro == kSoftcapGrad) ? 2 
           dst[k] = make_float4(v[4 * k], v[4 * k + 1], v[4 * k + 2], v[4 * k + 3]);
       }
     } else {
+      if constexpr (kPro != kNone) {
 #pragma unroll
-      for (int k = 0; k < 8; ++k) {
-        v[2 * k] = __uint_as_float(raw[it][k] << 16);
-        v[2 * k + 1] = __uint_as_float(raw[it][k] & 0xffff0000u);
+        for (int k = 0; k < 8; ++k) {
+          v[2 * k] = __uint_as_float(raw[it][k] << 16);
+          v[2 * k + 1] = __uint_as_float(raw[it][k] & 0xffff0000u);
+        }
       }
       if constexpr (kPro == kNone) {
-        // integer order of |bf16| patterns is float order; a NaN pattern shows up as the maximum and sends the
-        // whole warp through the float path, which skips NaNs as fmaxf does
-        m_bits = absmax_bits_bf16x16(raw[it]) << 16;
-        if (__any_sync(0xffffffffu, m_bits > 0x7f800000u)) {
-          float m = 0.f;
+        // the packed maximum skips NaN operands, as the reference's fmaxf does
+        uint32_t m = 0u;
 #pragma unroll
-          for (int k = 0; k < 16; ++k)
-            m = fmaxf(m, fabsf(v[k]));
-          m_bits = __float_as_uint(m);
-        }
+        for (int k = 0; k < 8; ++k)
+          m = max_abs_skip_nan_bf16x2(m, raw[it][k]);
+        m &= 0x7fff7fffu;
+        m_bits = max(m & 0xffffu, m >> 16) << 16;
         if (want_cols) {
           uint4* dst = reinterpret_cast<uint4*>(tile + r * kTile + c);
           dst[0] = make_uint4(raw[it][0], raw[it][1], raw[it][2], raw[it][3]);
@@ -263,12 +248,21 @@ __global__ void __launch_bounds__(kThreads, (kIn32 || kPro == kSoftcapGrad) ? 2 
       // non-negative float bits order as integers
       m_bits = max(m_bits, __shfl_xor_sync(0xffffffffu, m_bits, 1));
       const int e = mx_exponent(m_bits, p.floor_rule);
-      const float mul = __uint_as_float(mx_multiplier_bits(e));
       uint4 o;
-      o.x = cvt_e4m3x4(v[0] * mul, v[1] * mul, v[2] * mul, v[3] * mul);
-      o.y = cvt_e4m3x4(v[4] * mul, v[5] * mul, v[6] * mul, v[7] * mul);
-      o.z = cvt_e4m3x4(v[8] * mul, v[9] * mul, v[10] * mul, v[11] * mul);
-      o.w = cvt_e4m3x4(v[12] * mul, v[13] * mul, v[14] * mul, v[15] * mul);
+      if constexpr (!kIn32 && kPro == kNone) {
+        // the multiplier is a power of two: the packed bf16 product is exact wherever e4m3 can tell
+        const uint32_t mul2 = (mx_multiplier_bits(e) >> 16) * 0x10001u;
+        o.x = e4m3x4_scaled(raw[it][0], raw[it][1], mul2);
+        o.y = e4m3x4_scaled(raw[it][2], raw[it][3], mul2);
+        o.z = e4m3x4_scaled(raw[it][4], raw[it][5], mul2);
+        o.w = e4m3x4_scaled(raw[it][6], raw[it][7], mul2);
+      } else {
+        const float mul = __uint_as_float(mx_multiplier_bits(e));
+        o.x = cvt_e4m3x4(v[0] * mul, v[1] * mul, v[2] * mul, v[3] * mul);
+        o.y = cvt_e4m3x4(v[4] * mul, v[5] * mul, v[6] * mul, v[7] * mul);
+        o.z = cvt_e4m3x4(v[8] * mul, v[9] * mul, v[10] * mul, v[11] * mul);
+        o.w = cvt_e4m3x4(v[12] * mul, v[13] * mul, v[14] * mul, v[15] * mul);
+      }
       *reinterpret_cast<uint4*>(static_cast<unsigned char*>(p.out.data) + (row0 + r) * p.out.ld + col0 + c) = o;
       if ((t & 1) == 0)
         sc_rows[mx_scale_tile_offset(r, c >> 5)] = static_cast<unsigned char>(e);
@@ -304,30 +298,21 @@ __global__ void __launch_bounds__(kThreads, (kIn32 || kPro == kSoftcapGrad) ? 2 
 #pragma unroll
       for (int k = 0; k < 32; ++k)
         w[k] = *reinterpret_cast<const uint32_t*>(tile + (rb * 32 + k) * kTile + 2 * cp);
-      uint32_t m = w[0] & 0x7fff7fffu;
+      uint32_t m = 0u;
 #pragma unroll
-      for (int k = 1; k < 32; ++k)
-        m = max_u16x2(m, w[k] & 0x7fff7fffu);
-      uint32_t blo = (m & 0xffffu) << 16, bhi = m & 0xffff0000u;
-      if (__any_sync(0xffffffffu, blo > 0x7f800000u || bhi > 0x7f800000u)) {  // a NaN somewhere: skip NaNs as fmaxf
-        float mlo = 0.f, mhi = 0.f;
+      for (int k = 0; k < 32; ++k)
+        m = max_abs_skip_nan_bf16x2(m, w[k]);
+      m &= 0x7fff7fffu;
+      elo = mx_exponent((m & 0xffffu) << 16, p.floor_rule), ehi = mx_exponent(m & 0xffff0000u, p.floor_rule);
+      // both columns scaled at once: powers of two, so the packed bf16 products are exact wherever e4m3 can tell
+      const uint32_t mul2 = (mx_multiplier_bits(elo) >> 16) | (mx_multiplier_bits(ehi) & 0xffff0000u);
 #pragma unroll
-        for (int k = 0; k < 32; ++k) {
-          mlo = fmaxf(mlo, fabsf(__uint_as_float(w[k] << 16)));
-          mhi = fmaxf(mhi, fabsf(__uint_as_float(w[k] & 0xffff0000u)));
-        }
-        blo = __float_as_uint(mlo), bhi = __float_as_uint(mhi);
-      }
-      elo = mx_exponent(blo, p.floor_rule), ehi = mx_exponent(bhi, p.floor_rule);
-      const float mullo = __uint_as_float(mx_multiplier_bits(elo)), mulhi = __uint_as_float(mx_multiplier_bits(ehi));
+      for (int k = 0; k < 32; ++k)
+        w[k] = mul_bf16x2(w[k], mul2);
 #pragma unroll
       for (int k = 0; k < 8; ++k) {
-        wlo[k] = cvt_e4m3x4(__uint_as_float(w[4 * k] << 16) * mullo, __uint_as_float(w[4 * k + 1] << 16) * mullo,
-                            __uint_as_float(w[4 * k + 2] << 16) * mullo, __uint_as_float(w[4 * k + 3] << 16) * mullo);
-        whi[k] = cvt_e4m3x4(__uint_as_float(w[4 * k] & 0xffff0000u) * mulhi,
-                            __uint_as_float(w[4 * k + 1] & 0xffff0000u) * mulhi,
-                            __uint_as_float(w[4 * k + 2] & 0xffff0000u) * mulhi,
-                            __uint_as_float(w[4 * k + 3] & 0xffff0000u) * mulhi);
+        wlo[k] = cvt_e4m3x4(lo_f32(w[4 * k]), lo_f32(w[4 * k + 1]), lo_f32(w[4 * k + 2]), lo_f32(w[4 * k + 3]));
+        whi[k] = cvt_e4m3x4(hi_f32(w[4 * k]), hi_f32(w[4 * k + 1]), hi_f32(w[4 * k + 2]), hi_f32(w[4 * k + 3]));
       }
     }
     unsigned char* dst = static_cast<unsigned char*>(p.out_t.data) + (col0 + 2 * cp) * p.out_t.ld + row0 + rb * 32;
