@@ -68,32 +68,12 @@ __device__ __forceinline__ uint32_t e4m3x4_scaled(uint32_t w0, uint32_t w1, uint
   return e4m3x4_from_f32(lo_f32(a), hi_f32(a), lo_f32(b), hi_f32(b));
 }
 
-// running maximum of |x| over packed bf16, taken on the 15-bit magnitudes as unsigned integers: ordered like the
-// values, with NaN (above 0x7f80) on top
-__device__ __forceinline__ uint32_t max_abs_u16x2(uint32_t m, uint32_t w) {
-  uint32_t d;
-  asm("max.u16x2 %0, %1, %2;" : "=r"(d) : "r"(m), "r"(w & 0x7fff7fffu));
-  return d;
-}
-
 // Running maximum of |x| over packed bf16 that skips NaN as fmaxf does (a NaN operand returns the other one), one
 // instruction per word. The result's sign bits carry no meaning (xor of the operands' signs): mask them off at the end.
 __device__ __forceinline__ uint32_t max_abs_skip_nan_bf16x2(uint32_t m, uint32_t w) {
   uint32_t d;
   asm("max.xorsign.abs.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(m), "r"(w));
   return d;
-}
-
-// The block maximum as the quantizer defines it (fmaxf over |x|, which skips NaN) from the packed running maximum m
-// of `count` words: the fast path when no NaN was seen, else a second pass with fmaxf.
-__device__ __forceinline__ float amax_from_packed(uint32_t m, const uint32_t* words, int count) {
-  const uint32_t top = max(m & 0xffffu, m >> 16);
-  if (top <= 0x7f80u)
-    return __uint_as_float(top << 16);
-  float f = 0.f;
-  for (int k = 0; k < count; ++k)
-    f = fmaxf(f, fmaxf(fabsf(lo_f32(words[k])), fabsf(hi_f32(words[k]))));
-  return f;
 }
 
 }  // namespace mxb200

@@ -253,25 +253,17 @@ __global__ void __launch_bounds__(kThreads, 1) mxb200_residual_norm_mx_kernel(co
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
             w[k] = pack_bf16x2_rn(lo_f32(src[k]) * rstd, hi_f32(src[k]) * rstd);
-            m = max_abs_u16x2(m, w[k]);
+            m = max_abs_skip_nan_bf16x2(m, w[k]);
           }
           tile_row[it * 32] = make_uint4(w[0], w[1], w[2], w[3]);
         }
-        // the block's 4 lanes agree on the packed maximum; a NaN anywhere in the warp (above 0x7f80) sends the whole
-        // warp through fmaxf, which skips NaN as the quantizer's maximum does
+        // the packed maximum skips NaN as the quantizer's fmaxf does; the block's 4 lanes then agree on it (magnitudes
+        // of bf16 order as unsigned integers)
+        m &= 0x7fff7fffu;
         uint32_t mm = max(m & 0xffffu, m >> 16);
         mm = max(mm, __shfl_xor_sync(0xffffffffu, mm, 1));
         mm = max(mm, __shfl_xor_sync(0xffffffffu, mm, 2));
-        float amax = __uint_as_float(mm << 16);
-        if (__any_sync(0xffffffffu, mm > 0x7f80u)) {
-          float f = 0.f;
-#pragma unroll
-          for (int k = 0; k < 4; ++k)
-            f = fmaxf(f, fmaxf(fabsf(lo_f32(w[k])), fabsf(hi_f32(w[k]))));
-          f = fmaxf(f, __shfl_xor_sync(0xffffffffu, f, 1));
-          f = fmaxf(f, __shfl_xor_sync(0xffffffffu, f, 2));
-          amax = f;
-        }
+        const float amax = __uint_as_float(mm << 16);
         if (active) {
           const int e = mx_exponent(__float_as_uint(amax), false);
           const uint32_t mul2 = (mx_multiplier_bits(e) >> 16) * 0x10001u;
@@ -302,9 +294,10 @@ __global__ void __launch_bounds__(kThreads, 1) mxb200_residual_norm_mx_kernel(co
         const uint32_t even = *reinterpret_cast<const unsigned short*>(tile + (2 * k) * pitch + c);
         const uint32_t odd = *reinterpret_cast<const unsigned short*>(tile + (2 * k + 1) * pitch + c);
         w[k] = even | (odd << 16);
-        m = max_abs_u16x2(m, w[k]);
+        m = max_abs_skip_nan_bf16x2(m, w[k]);
       }
-      const float amax = amax_from_packed(m, w, kRows / 2);
+      m &= 0x7fff7fffu;
+      const float amax = __uint_as_float(max(m & 0xffffu, m >> 16) << 16);
       const int e = mx_exponent(__float_as_uint(amax), false);
       const uint32_t mul2 = (mx_multiplier_bits(e) >> 16) * 0x10001u;
       uint32_t q[8];
