@@ -12,7 +12,7 @@ distributions; there is no dataset or checkpoint on this path.
 value: GEMM TFLOP/s of the whole job (all ranks), from device time of the timed steps, inputs resident in HBM.
 The steps are then run a second time with CUDA events around every launch, which gives the per-kernel durations.
 e2e: the same with each step's micro-batch activations copied from pinned host memory inside the timed region
-and a slice of the result read back. roofline: the GEMM kernel alone, bracketed by CUDA events on its stream.
+(on a copy stream, one step ahead, as a loader would) and a slice of the result read back every step. roofline: the GEMM kernel alone, bracketed by CUDA events on its stream.
 cpu_baseline / --impl reference: the reference's CPU formulation of the path (libtorch quantize -> dequantize ->
 fp32 matmul, oracle/torch_reference.py) on a bounded sample, on the host cores.
 """
@@ -226,25 +226,45 @@ def run_gpu_arm(args):
     n_quant = len(quant_events) // 2
     watchdog = nc.capi.device_status()
 
-    # ---- end to end: the step's micro-batch activations come from pinned host memory, a result slice goes back
-    host_in = [t.cpu().pin_memory() for t in (step.x_attn[0], step.y_att[0], step.x_mlp[0])]
+    # ---- end to end: every step's micro-batch activations come from pinned host memory and a result slice goes back.
+    # As a training loop's loader would, the copy of step i + 1's inputs runs on a copy stream into staging buffers
+    # while step i computes; the step then takes them with a device-side copy. All of it is inside the timed region.
+    targets = (step.x_attn[0], step.y_att[0], step.x_mlp[0])
+    host_in = [t.cpu().pin_memory() for t in targets]
+    staging = [torch.empty_like(t) for t in targets]
     host_out = torch.empty(4096, dtype=torch.bfloat16).pin_memory()
     h2d = sum(t.numel() * t.element_size() for t in host_in)
     d2h = host_out.numel() * host_out.element_size()
+    copy_stream = torch.cuda.Stream(device=device)
+    staged = torch.cuda.Event()
+    taken = torch.cuda.Event()
 
-    def e2e_step(i):
-        for dst, src in zip((step.x_attn[0], step.y_att[0], step.x_mlp[0]), host_in):
-            dst.copy_(src, non_blocking=True)
+    def prefetch():
+        copy_stream.wait_event(taken)  # the staging buffers' previous contents have been consumed
+        with torch.cuda.stream(copy_stream):
+            for dst, src in zip(staging, host_in):
+                dst.copy_(src, non_blocking=True)
+            staged.record()
+
+    def e2e_step(i, last):
+        torch.cuda.current_stream().wait_event(staged)
+        for dst, src in zip(targets, staging):
+            dst.copy_(src)
+        taken.record()
+        if not last:
+            prefetch()
         step.run_step(0)
         host_out.copy_((step.bucket.shards[0] if world > 1 else step.bucket.buffer)[:4096], non_blocking=True)
         torch.cuda.current_stream().synchronize()
 
-    e2e_step(0)
+    taken.record()
+    prefetch()
+    e2e_step(0, False)
     barrier()
     e_begin, e_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e_begin.record()
     for i in range(args.steps):
-        e2e_step(i)
+        e2e_step(i, i == args.steps - 1)
     e_end.record()
     barrier()
     e2e_ms = e_begin.elapsed_time(e_end)
