@@ -34,7 +34,8 @@ METRIC = "MXFP8 linear TFLOP/s/GPU, d24 fwd+dgrad+wgrad shapes, % of FP8 tensor 
 WORKLOAD = "d24 data-parallel step GEMM set: 24 x (QKV, attn-out, MLP fc, MLP proj) + lm_head in 2048-row chunks, fwd+dgrad+wgrad, M=16384 tokens/rank"
 FP8_SPEC_TFLOPS = 4500.0  # B200 dense FP8, 2x the 2.25e15 bf16 figure
 # dram__bytes_read.sum + dram__bytes_write.sum of one captured launch of the GEMM kernel, the merged-QKV forward
-# (M=16384, N=4608, K=1536, bf16 out): profiles/gemm_pair_kernel_d24_shapes.md. Its algorithmic bytes: 184.3e6.
+# (M=16384, N=4608, K=1536, bf16 out), from the ncu summary of the pair kernel kept under profiles/. Its algorithmic
+# bytes: 184.3e6.
 GEMM_TRAFFIC_BYTES = 171.8e6
 GEMM_TRAFFIC_LAUNCH = "qkv.fwd 16384x4608x1536 (algorithmic 184.3 MB; the step's other launches differ in shape)"
 
