@@ -42,6 +42,12 @@ __device__ uint32_t g_watchdog_word;
 // cudaGetSymbolAddress, never a device pointer.
 static __device__ __align__(256) unsigned char g_static_splitk_scratch[MXB200_STATIC_SCRATCH_BYTES];
 
+// Work counters of the CTA-pair kernel's tile scheduler: {next unit, pairs done} per launch slot, zero between
+// launches (the last pair to finish a launch zeroes its slot). Launches take slots round-robin, so kernels that
+// overlap on one device (different streams) do not share one.
+constexpr int kSchedLaunchSlots = 64;
+__device__ uint32_t g_sched_words[2 * kSchedLaunchSlots];
+
 #ifdef MXB200_TRACE
 // Development aid (never compiled into the shipped library): per-tile timestamps of the first CTA pair.
 __device__ unsigned long long g_trace[8192];
@@ -77,6 +83,8 @@ enum WaitSite : uint32_t {
   kSiteMmaOverlap = 4,
   kSiteEpilogueFull = 5,
   kSiteEpilogueSync = 6,
+  kSiteSchedEmpty = 7,
+  kSiteSchedFull = 8,
 };
 
 template <int BN>
@@ -93,7 +101,7 @@ struct Config {
   static constexpr uint32_t kSfaCol = kOverlap ? 480 : 2 * BN;
   static constexpr uint32_t kSfbCol = kSfaCol + 4;
   static constexpr size_t kSmemBytes =
-        1024 /* alignment slack */ + static_cast<size_t>(kStages) * (kABytes + kBBytes + kSfBytes) + 256 /* barriers */;
+        1024 /* alignment slack */ + static_cast<size_t>(kStages) * (kABytes + kBBytes + kSfBytes) + 512 /* barriers */;
 };
 
 struct GemmParams {
@@ -120,6 +128,7 @@ struct GemmParams {
   int q_scale_tiles, qt_scale_tiles;
   const void* h_in;
   bool floor_rule;
+  int sched_slot;  // CTA-pair kernel: this launch's pair of words in g_sched_words
 };
 
 struct Barriers {
@@ -132,7 +141,13 @@ struct Barriers {
   uint32_t tmem_base;
   uint32_t abort_flag;
   uint32_t last_flag;
+  // CTA-pair kernel, tile scheduler: the leader CTA's producer draws unit indices from a global counter and posts each
+  // to both CTAs (sched_unit, sched_full); every other role of the pair reads it and reports to the leader's sched_empty
+  uint64_t sched_full[4];
+  uint64_t sched_empty[4];
+  uint32_t sched_unit[4];
 };
+constexpr int kSchedSlots = 4;
 
 __device__ __forceinline__ bool wait_bounded(uint64_t* bar, uint32_t parity, Barriers* bars, uint32_t site) {
   if (mbar_try_wait(bar, parity))
@@ -798,6 +813,34 @@ __device__ __forceinline__ void fused_quantize_chunk(const GemmParams& p, const 
 
 // ------------------------------------------------------------------------------------------------ CTA-pair kernel
 //
+// Tile scheduler. The persistent pairs do not stride through the unit list: the leader CTA's producer warp draws the
+// next unit from a global counter (one unit ahead, so the atomic's latency hides behind a tile's loads) and posts it
+// in a 4-slot ring in both CTAs' shared memory; the other roles (peer producer, MMA warp, all epilogue warps) read
+// each posting in order. A pair that starts late, because its SMs were busy with another kernel (a collective's
+// CTAs on a side stream, say), then simply takes fewer units instead of holding the whole launch back with a fixed
+// share. A drawn index at or past the number of units is the stop sign; the last pair to see it zeroes the counters
+// for the next launch.
+
+// One reader's step: waits for posting number `seq`, returns its unit, and frees the slot for this reader. Called by a
+// whole warp. `arm`: this warp arms the peer CTA's copy of the barrier for the remote store (peer producer only).
+__device__ __forceinline__ bool sched_read(Barriers* bars, uint32_t seq, bool arm, uint32_t empty_leader0, int lane,
+                                           int* unit) {
+  const uint32_t slot = seq & (kSchedSlots - 1), parity = (seq / kSchedSlots) & 1u;
+  if (arm) {
+    mbar_arrive_expect_tx(lane == 0 ? 1u : 0u, &bars->sched_full[slot], 4);
+    __syncwarp();
+  }
+  if (!wait_bounded_warp(&bars->sched_full[slot], parity, bars, kSiteSchedFull))
+    return false;
+  int u = static_cast<int>(*reinterpret_cast<volatile uint32_t*>(&bars->sched_unit[slot]));
+  u = __shfl_sync(0xffffffffu, u, 0);  // lane 0's load has returned before its arrival below is issued
+  if (lane == 0)
+    mbar_arrive_cluster(empty_leader0 + slot * 8);
+  *unit = u;
+  return true;
+}
+
+//
 // Two CTAs on the SMs of one TPC (a cluster of 2) share one 256 x 256 output tile: tcgen05.mma.cta_group::2 reads
 // 128 rows of A and 128 rows of B from each CTA's shared memory and leaves each CTA its own 128 rows of the
 // accumulator in its own TMEM. Per K step every CTA therefore loads 16 KB of A and 16 KB of B for 128 x 256 x 128
@@ -844,8 +887,9 @@ struct PairConfig {
   static constexpr uint32_t kAcc0 = 0, kAcc1 = kOverlap ? 224 : TN;
   static constexpr uint32_t kSfaCol = kOverlap ? 480 : 2 * TN, kSfbCol = kSfaCol + 4;
   static constexpr size_t kSmemBytes = 1024 + static_cast<size_t>(kStages) * (kABytes + kBBytes + kSfBytes) +
-                                       kEpiWarps * kEpiBytes + 256;
+                                       kEpiWarps * kEpiBytes + 512;
   static_assert(kSmemBytes <= 232448, "shared memory per CTA");
+  static_assert(sizeof(Barriers) <= 512, "barrier block");
 };
 
 template <int TN, int kFuse>
@@ -869,7 +913,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairConfig<TN, kFuse
   const int warp = static_cast<int>(threadIdx.x) >> 5, lane = static_cast<int>(threadIdx.x) & 31;
   const uint32_t rank = cluster_ctarank();
   const bool leader = rank == 0;
-  const int pair = static_cast<int>(blockIdx.x) >> 1, num_pairs = static_cast<int>(gridDim.x) >> 1;
+  const int num_pairs = static_cast<int>(gridDim.x) >> 1;
   const int total_units = p.tiles_m * p.tiles_n * p.splits;
 
   if (threadIdx.x == 0) {
@@ -883,6 +927,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairConfig<TN, kFuse
     }
     mbar_init(&bars->overlap_free, 8);  // the four warps per CTA that own the shared columns
     mbar_init(&bars->epi_sync, C::kEpiThreads);
+    for (int i = 0; i < kSchedSlots; ++i) {
+      mbar_init(&bars->sched_full[i], 1);
+      // readers of a posted unit: the MMA warp, the peer's producer, and both CTAs' epilogue warps (leader's copy)
+      mbar_init(&bars->sched_empty[i], 2 * C::kEpiWarps + 2);
+    }
     bars->abort_flag = 0;
     bars->last_flag = 0;
     fence_mbar_init();
@@ -923,14 +972,47 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairConfig<TN, kFuse
       const uint32_t full_leader0 = map_to_cta(full0, 0);
       uint32_t stage = 0, phase = 0;
       bool ok = true;
-      for (int unit = pair; ok && unit < total_units; unit += num_pairs) {
+      uint32_t* const sched = g_sched_words + 2 * p.sched_slot;
+      const uint32_t sched_empty_leader0 = map_to_cta(smem_u32(&bars->sched_empty[0]), 0);
+      const uint32_t sched_full_peer0 = map_to_cta(smem_u32(&bars->sched_full[0]), 1);
+      const uint32_t sched_unit_peer0 = map_to_cta(smem_u32(&bars->sched_unit[0]), 1);
+      int drawn = 0;  // leader: the unit drawn for the next posting
+      if (leader) {
+        if (lane == 0)
+          drawn = static_cast<int>(atomicAdd(&sched[0], 1u));
+        drawn = __shfl_sync(0xffffffffu, drawn, 0);
+      }
+      for (uint32_t seq = 0; ok; ++seq) {
+        int unit;
+        if (leader) {
+          // post the drawn unit to both CTAs once every reader is done with the slot's previous posting
+          const uint32_t slot = seq & (kSchedSlots - 1), parity = (seq / kSchedSlots) & 1u;
+          if (!wait_bounded_warp(&bars->sched_empty[slot], parity ^ 1u, bars, kSiteSchedEmpty)) {
+            ok = false;
+            break;
+          }
+          unit = drawn;
+          if (lane == 0) {
+            *reinterpret_cast<volatile uint32_t*>(&bars->sched_unit[slot]) = static_cast<uint32_t>(unit);
+            mbar_arrive(&bars->sched_full[slot]);  // release: the store above is visible to this CTA's readers
+            st_async_u32(sched_unit_peer0 + slot * 4, static_cast<uint32_t>(unit), sched_full_peer0 + slot * 8);
+            if (unit < total_units)  // draw one ahead: the round trip overlaps this unit's loads
+              drawn = static_cast<int>(atomicAdd(&sched[0], 1u));
+          }
+          __syncwarp();
+        } else if (!sched_read(bars, seq, true, sched_empty_leader0, lane, &unit)) {
+          ok = false;
+          break;
+        }
+        if (unit >= total_units)
+          break;
         const TileCoord tc = decode_unit(p, unit);
         const int k_begin = tc.split * p.k_tiles_split;
         const int k_end = min(k_begin + p.k_tiles_split, p.k_tiles_total);
         const int row_a = tc.m * C::kTileM + static_cast<int>(rank) * 128;
         const int row_b = tc.n * C::kTileN + static_cast<int>(rank) * C::kBRows;
         const int sfa_tile = row_a >> 7, sfb_tile = (tc.n * C::kTileN) >> 7;
-        if (el) TRACE(4, (unit - pair) / num_pairs);
+        if (el) TRACE(4, seq);
         for (int kt = k_begin; kt < k_end; ++kt) {
           if (!wait_bounded_warp(empty0 + stage * 8, phase ^ 1u, bars, kSiteProducerEmpty)) {
             ok = false;
@@ -948,6 +1030,14 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairConfig<TN, kFuse
             phase ^= 1u;
           }
         }
+        if (leader)
+          drawn = __shfl_sync(0xffffffffu, drawn, 0);
+      }
+      // the launch's last pair leaves the counters at zero for the next launch that takes this slot; every pair's
+      // final draw (the one past the end) has happened before it counts itself done
+      if (leader && ok && lane == 0 && atomicAdd(&sched[1], 1u) == static_cast<uint32_t>(num_pairs) - 1u) {
+        sched[0] = 0;
+        sched[1] = 0;
       }
     }
   } else if (warp == 1) {
@@ -965,7 +1055,15 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairConfig<TN, kFuse
       const uint64_t a_desc0 = make_smem_desc(smem_u32(s_a), 16, 1024, 2);
       const uint64_t b_desc0 = make_smem_desc(smem_u32(s_b), 16, 1024, 2);
       const uint64_t sf_desc0 = make_smem_desc(smem_u32(s_sf), 0, 128, 0);
-      for (int unit = pair; ok && unit < total_units; unit += num_pairs, ++local) {
+      const uint32_t sched_empty_leader0 = map_to_cta(smem_u32(&bars->sched_empty[0]), 0);
+      for (; ok; ++local) {
+        int unit;
+        if (!sched_read(bars, local, false, sched_empty_leader0, lane, &unit)) {
+          ok = false;
+          break;
+        }
+        if (unit >= total_units)
+          break;
         const TileCoord tc = decode_unit(p, unit);
         const uint32_t buf = local & 1u, use = local >> 1;
         if (!wait_bounded_warp(&bars->tmem_empty[buf], (use & 1u) ^ 1u, bars, kSiteMmaTmemEmpty)) {
@@ -1037,7 +1135,15 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairConfig<TN, kFuse
                                       map_to_cta(smem_u32(&bars->tmem_empty[1]), 0)};
     const uint32_t overlap_leader = map_to_cta(smem_u32(&bars->overlap_free), 0);
     unsigned char* stage = s_epi + (warp - 2) * C::kEpiBytes;
-    for (int unit = pair; ok && unit < total_units; unit += num_pairs, ++local) {
+    const uint32_t sched_empty_leader0 = map_to_cta(smem_u32(&bars->sched_empty[0]), 0);
+    for (; ok; ++local) {
+      int unit;
+      if (!sched_read(bars, local, false, sched_empty_leader0, lane, &unit)) {
+        ok = false;
+        break;
+      }
+      if (unit >= total_units)
+        break;
       const TileCoord tc = decode_unit(p, unit);
       const uint32_t buf = local & 1u, use = local >> 1;
       // the relu^2 backward form reads h: the first chunk's block is requested before the accumulator is waited for
@@ -1483,6 +1589,8 @@ int gemm(const void* a, const void* a_scale, const void* b, const void* b_scale,
         return st;
     }
     const int pairs = static_cast<int>(std::min<int64_t>(tiles * p.splits, std::max(cap / 2, 1)));
+    static std::atomic<uint32_t> launch_seq{0};
+    p.sched_slot = static_cast<int>(launch_seq.fetch_add(1, std::memory_order_relaxed) % kSchedLaunchSlots);
     if (fused.fuse == kFuseReluSquare)
       return launch_pair_width<kFuseReluSquare>(plan.tile_n, m, p, pairs, s);
     if (fused.fuse == kFuseReluSquareBwd)

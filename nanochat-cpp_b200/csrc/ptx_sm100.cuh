@@ -267,6 +267,14 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
   asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 
+// A 4-byte store into another CTA's shared memory that completes 4 bytes of a transaction on an mbarrier of that CTA
+// (both addresses from map_to_cta): a thread that sees that barrier's phase complete sees the value, as with TMA data.
+__device__ __forceinline__ void st_async_u32(uint32_t cluster_addr, uint32_t value, uint32_t cluster_bar) {
+  asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.b32 [%0], %1, [%2];"
+               ::"r"(cluster_addr), "r"(value), "r"(cluster_bar)
+               : "memory");
+}
+
 // Tiled loads for a CTA pair: data lands in the issuing CTA's shared memory, the byte count is credited to an
 // mbarrier that may live in the pair's other CTA (cluster address).
 __device__ __forceinline__ void tma_load_2d_pair(uint32_t pred, uint32_t smem_dst, const CUtensorMap* map,
