@@ -300,3 +300,39 @@ def test_relu_square_bwd_gemm_matches_unfused(M, N, K, tile_n):
     for name in ("data", "inv_scale", "data_t", "inv_scale_t"):
         gt, w = getattr(got, name).view(torch.uint8), getattr(want, name).view(torch.uint8)
         assert torch.equal(gt, w), f"{name}: {(gt != w).sum().item()} bytes differ"
+
+
+@pytest.mark.parametrize("max_ctas", [2, 6, 50])
+def test_tile_scheduler_with_few_pairs(max_ctas):
+    """The CTA-pair kernel's pairs draw their tiles from a global counter: with the launch capped to a few CTAs each
+    pair walks many tiles, and the result is the same bits as with the whole machine."""
+    M, N, K = 1024, 1280, 512
+    qa, qb = quantized(M, N, K, seed=21)
+    full = nc.mx_gemm(qa.data, qa.inv_scale, qb.data, qb.inv_scale, torch.bfloat16)
+    nc.capi.lib.mxb200_set_gemm_config(0, max_ctas)
+    few = nc.mx_gemm(qa.data, qa.inv_scale, qb.data, qb.inv_scale, torch.bfloat16)
+    assert torch.equal(few, full)
+    assert rel(few.float().cpu(), oracle_product(qa, qb)) < TOL_BF16
+    f32 = nc.mx_gemm(qa.data, qa.inv_scale, qb.data, qb.inv_scale, torch.float32, splits=2)
+    assert rel(f32.cpu(), oracle_product(qa, qb)) < TOL_F32
+
+
+def test_overlapping_launches_on_two_streams():
+    """Launches that overlap on the device take different scheduler counters: two streams of GEMMs of different
+    shapes, 30 launches each, give what the same launches give one after another."""
+    qa1, qb1 = quantized(2048, 1024, 512, seed=22)
+    qa2, qb2 = quantized(1024, 1536, 1024, seed=23)
+    want1 = nc.mx_gemm(qa1.data, qa1.inv_scale, qb1.data, qb1.inv_scale, torch.bfloat16)
+    want2 = nc.mx_gemm(qa2.data, qa2.inv_scale, qb2.data, qb2.inv_scale, torch.bfloat16)
+    torch.cuda.synchronize()
+    s1, s2 = torch.cuda.Stream(), torch.cuda.Stream()
+    outs1 = [torch.empty_like(want1) for _ in range(30)]
+    outs2 = [torch.empty_like(want2) for _ in range(30)]
+    for i in range(30):
+        with torch.cuda.stream(s1):
+            nc.mx_gemm_out(outs1[i], qa1.data, qa1.inv_scale, qb1.data, qb1.inv_scale)
+        with torch.cuda.stream(s2):
+            nc.mx_gemm_out(outs2[i], qa2.data, qa2.inv_scale, qb2.data, qb2.inv_scale)
+    torch.cuda.synchronize()
+    assert all(torch.equal(o, want1) for o in outs1)
+    assert all(torch.equal(o, want2) for o in outs2)
