@@ -36,7 +36,7 @@ FP8_SPEC_TFLOPS = 4500.0  # B200 dense FP8, 2x the 2.25e15 bf16 figure
 # dram__bytes_read.sum + dram__bytes_write.sum of one captured launch of the GEMM kernel, the merged-QKV forward
 # (M=16384, N=4608, K=1536, bf16 out), from the ncu summary of the pair kernel kept under profiles/. Its algorithmic
 # bytes: 184.3e6.
-GEMM_TRAFFIC_BYTES = 171.8e6
+GEMM_TRAFFIC_BYTES = 167.5e6
 GEMM_TRAFFIC_LAUNCH = "qkv.fwd 16384x4608x1536 (algorithmic 184.3 MB; the step's other launches differ in shape)"
 
 
