@@ -1674,6 +1674,9 @@ extern "C" int mxb200_device_status(uint32_t* word) {
   if (w != 0) {
     const uint32_t zero = 0;
     cudaMemcpyToSymbol(mxb200::g_watchdog_word, &zero, sizeof(zero));
+    // a launch that gave up did not finish its tile list: its scheduler counters are left mid-way
+    static const uint32_t zeros[2 * mxb200::kSchedLaunchSlots] = {};
+    cudaMemcpyToSymbol(mxb200::g_sched_words, zeros, sizeof(zeros));
   }
   if (const uint32_t norm = mxb200::take_norm_watchdog_word(); w == 0)
     w = norm;
