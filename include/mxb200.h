@@ -68,6 +68,21 @@ typedef struct mxb200_mx_out {
 MXB200_API int mxb200_quantize_mx(const void* x, int x_bf16, int64_t rows, int64_t cols, mxb200_mx_out out, mxb200_mx_out out_t,
                        int prologue, int scale_rule, void* stream);
 
+/* One tensor of mxb200_quantize_mx_batch: the arguments of mxb200_quantize_mx that differ per tensor. */
+typedef struct mxb200_quantize_job {
+  const void* x;
+  int64_t rows, cols;
+  mxb200_mx_out out, out_t;
+} mxb200_quantize_job;
+
+/* mxb200_quantize_mx (no prologue) of n_jobs tensors of one input type in as few launches as possible (32 tensors
+ * each), bit for bit what n_jobs separate calls give. It stands for the runs of quantize_mx calls the reference makes
+ * on small tensors: the three parts of the merged q/k/v weight (src/nanochat/model/fp8/fp8.cpp:155-171) and a model's
+ * weights after an optimizer step (Fp8WeightCache, fp8.cpp:516-536), where a launch per matrix of one or two waves of
+ * tiles is bound by its own ramp-up and tail. jobs is read on the host during the call. */
+MXB200_API int mxb200_quantize_mx_batch(const mxb200_quantize_job* jobs, int n_jobs, int x_bf16, int scale_rule,
+                                        void* stream);
+
 /* Replaces nanochat::kernels::quantize_mx_relu_square_bwd (fp8_kernel.h:41-43, fp8_kernel.cu:207-210):
  * quantizes dh = bf16(h > 0 ? g * 2h : 0) from bf16 g, h (rows, cols) without writing dh. */
 MXB200_API int mxb200_quantize_mx_relu_square_bwd(const void* g, const void* h, int64_t rows, int64_t cols, mxb200_mx_out out,

@@ -20,7 +20,7 @@ STATIC_SCRATCH_BYTES = 32 << 20
 
 # every symbol include/mxb200.h declares
 SYMBOLS = (
-    "mxb200_quantize_mx", "mxb200_quantize_mx_relu_square_bwd", "mxb200_gemm_bf16", "mxb200_gemm_f32",
+    "mxb200_quantize_mx", "mxb200_quantize_mx_batch", "mxb200_quantize_mx_relu_square_bwd", "mxb200_gemm_bf16", "mxb200_gemm_f32",
     "mxb200_gemm_relu_square", "mxb200_gemm_relu_square_bwd", "mxb200_residual_norm_mx_fwd",
     "mxb200_softcap_ce_loss", "mxb200_softcap_ce_grad_mx",
     "mxb200_gemm_splits", "mxb200_gemm_workspace_bytes", "mxb200_gemm_splitk", "mxb200_gemm_splitk_static",
@@ -33,6 +33,12 @@ class MxOut(ctypes.Structure):
     """mxb200_mx_out / nanochat::kernels::MxOut."""
     _fields_ = [("data", ctypes.c_void_p), ("ld", ctypes.c_int64), ("scale", ctypes.c_void_p),
                 ("scale_tiles", ctypes.c_int64)]
+
+
+class QuantizeJob(ctypes.Structure):
+    """mxb200_quantize_job."""
+    _fields_ = [("x", ctypes.c_void_p), ("rows", ctypes.c_int64), ("cols", ctypes.c_int64), ("out", MxOut),
+                ("out_t", MxOut)]
 
 
 class ResidualNormMx(ctypes.Structure):
@@ -56,6 +62,7 @@ def _load() -> ctypes.CDLL:
     lib = ctypes.CDLL(LIB_PATH)
     vp, i64, i32 = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int
     lib.mxb200_quantize_mx.argtypes = [vp, i32, i64, i64, MxOut, MxOut, i32, i32, vp]
+    lib.mxb200_quantize_mx_batch.argtypes = [ctypes.POINTER(QuantizeJob), i32, i32, i32, vp]
     lib.mxb200_quantize_mx_relu_square_bwd.argtypes = [vp, vp, i64, i64, MxOut, MxOut, i32, vp]
     lib.mxb200_gemm_bf16.argtypes = [vp, vp, vp, vp, vp, vp, i64, i64, i64, vp]
     lib.mxb200_gemm_f32.argtypes = [vp, vp, vp, vp, vp, i64, i64, i64, vp, i32, vp]

@@ -121,9 +121,9 @@ __device__ __forceinline__ void load_u32x8_stream(const void* p, uint32_t (&w)[8
 // kIn32: fp32 input (parked as float), else bf16 (parked as bf16).
 // Row pass: a thread owns 16 consecutive values of a row (one 256-bit load of bf16), two lanes share a 32-value
 // block (one shuffle), 16 E4M3 bytes leave with one 128-bit store (512 contiguous bytes per warp).
+// One CTA's work: tile number `tile_index` (row-major over the tensor's 128 x 128 tiles) of the tensor p describes.
 template <bool kIn32, int kPro>
-__global__ void __launch_bounds__(kThreads, (kIn32 || kPro == kSoftcapGrad) ? 2 : (kPro == kReluSquareBwd ? 3 : 4))
-      mxb200_quantize_kernel(const QuantParams p) {
+__device__ __forceinline__ void quantize_tile(const QuantParams& p, int tile_index) {
   using Park = typename std::conditional<kIn32, float, __nv_bfloat16>::type;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   Park* tile = reinterpret_cast<Park*>(smem_raw);                               // [128][128]
@@ -131,7 +131,7 @@ __global__ void __launch_bounds__(kThreads, (kIn32 || kPro == kSoftcapGrad) ? 2 
   unsigned char* sc_cols = sc_rows + kScaleTileBytes;                           // 512 B, swizzled
 
   const int t = static_cast<int>(threadIdx.x);
-  const int tile_r = static_cast<int>(blockIdx.x) / p.tiles_c, tile_c = static_cast<int>(blockIdx.x) % p.tiles_c;
+  const int tile_r = tile_index / p.tiles_c, tile_c = tile_index % p.tiles_c;
   const int64_t row0 = static_cast<int64_t>(tile_r) * kTile, col0 = static_cast<int64_t>(tile_c) * kTile;
   const bool want_rows = p.out.data != nullptr, want_cols = p.out_t.data != nullptr;
 
@@ -337,6 +337,44 @@ __global__ void __launch_bounds__(kThreads, (kIn32 || kPro == kSoftcapGrad) ? 2 
   }
 }
 
+template <bool kIn32, int kPro>
+__global__ void __launch_bounds__(kThreads, (kIn32 || kPro == kSoftcapGrad) ? 2 : (kPro == kReluSquareBwd ? 3 : 4))
+      mxb200_quantize_kernel(const QuantParams p) {
+  quantize_tile<kIn32, kPro>(p, static_cast<int>(blockIdx.x));
+}
+
+// Several tensors in one launch: a weight matrix of a d12-d26 model is 36 to 700 tiles, under one or two waves of
+// the machine, so a launch per weight is bound by its own ramp-up and tail (12 us for 14 MB). The tiles of up to
+// kMaxBatch tensors are numbered through; a CTA finds its tensor by its first tile.
+constexpr int kMaxBatch = 32;
+
+struct BatchJob {
+  const void* x;
+  int64_t ld;
+  mxb200_mx_out out, out_t;
+  int tiles_c;
+  int first_tile;
+  bool wide_in, wide_out_t;
+};
+
+struct BatchParams {
+  BatchJob jobs[kMaxBatch];
+  int n;
+  bool floor_rule;
+};
+
+template <bool kIn32>
+__global__ void __launch_bounds__(kThreads, kIn32 ? 2 : 4) mxb200_quantize_batch_kernel(const __grid_constant__ BatchParams bp) {
+  int j = 0;
+  const int tile = static_cast<int>(blockIdx.x);
+  while (j + 1 < bp.n && tile >= bp.jobs[j + 1].first_tile)
+    ++j;
+  const BatchJob& job = bp.jobs[j];
+  QuantParams p{job.x,      nullptr,         job.ld, job.out, job.out_t, job.tiles_c, bp.floor_rule,
+                job.wide_in, job.wide_out_t, SoftcapGrad{}};
+  quantize_tile<kIn32, kNone>(p, tile - job.first_tile);
+}
+
 int check_out(const mxb200_mx_out& o, int64_t ld_min) {
   if (o.data == nullptr)
     return MXB200_OK;
@@ -415,9 +453,84 @@ int quantize(const void* x, const void* h, bool x_bf16, int64_t rows, int64_t co
   }
 }
 
+template <bool kIn32>
+int launch_batch(const BatchParams& bp, int tiles, cudaStream_t stream) {
+  constexpr size_t smem = (kIn32 ? 4 : 2) * kTile * kTile + 2 * kScaleTileBytes;
+  static std::atomic<int> configured_for{-1};
+  int device = 0;
+  cudaGetDevice(&device);
+  if (smem > 48 * 1024 && configured_for.load() != device) {
+    if (cudaFuncSetAttribute(mxb200_quantize_batch_kernel<kIn32>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(smem)) != cudaSuccess)
+      return MXB200_ERR_LAUNCH;
+    configured_for.store(device);
+  }
+  mxb200_quantize_batch_kernel<kIn32><<<static_cast<unsigned>(tiles), kThreads, smem, stream>>>(bp);
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return launch_status();
+}
+
+int quantize_batch(const mxb200_quantize_job* jobs, int n_jobs, bool x_bf16, int scale_rule, void* stream) {
+  DeviceInfo dev;
+  if (int s = current_device(&dev); s != MXB200_OK)
+    return s;
+  if (n_jobs < 0 || (n_jobs > 0 && jobs == nullptr))
+    return MXB200_ERR_NULL;
+  if (scale_rule != MXB200_SCALE_REFERENCE && scale_rule != MXB200_SCALE_OCP_FLOOR)
+    return MXB200_ERR_ARGUMENT;
+  // every job is checked before anything is launched
+  for (int i = 0; i < n_jobs; ++i) {
+    const mxb200_quantize_job& j = jobs[i];
+    if (j.x == nullptr)
+      return MXB200_ERR_NULL;
+    if (j.rows <= 0 || j.cols <= 0 || j.rows % kTile != 0 || j.cols % kTile != 0 ||
+        j.rows * j.cols / (kTile * kTile) > 0x3fffffffLL)
+      return MXB200_ERR_SHAPE;
+    if (!aligned16(j.x))
+      return MXB200_ERR_ALIGNMENT;
+    if (int s = check_out(j.out, j.cols); s != MXB200_OK)
+      return s;
+    if (int s = check_out(j.out_t, j.rows); s != MXB200_OK)
+      return s;
+  }
+  auto* s = static_cast<cudaStream_t>(stream);
+  int i = 0;
+  while (i < n_jobs) {
+    BatchParams bp{};
+    bp.floor_rule = scale_rule == MXB200_SCALE_OCP_FLOOR;
+    int64_t tiles = 0;
+    while (i < n_jobs && bp.n < kMaxBatch) {
+      const mxb200_quantize_job& j = jobs[i];
+      const int64_t mine = (j.rows / kTile) * (j.cols / kTile);
+      if (j.out.data == nullptr && j.out_t.data == nullptr) {  // nothing asked of this one
+        ++i;
+        continue;
+      }
+      if (tiles + mine > 0x7fffffffLL)
+        break;
+      bp.jobs[bp.n++] = BatchJob{j.x, j.cols, j.out, j.out_t, static_cast<int>(j.cols / kTile), static_cast<int>(tiles),
+                                 (reinterpret_cast<uintptr_t>(j.x) & 31u) == 0,
+                                 (reinterpret_cast<uintptr_t>(j.out_t.data) & 31u) == 0 && j.out_t.ld % 32 == 0};
+      tiles += mine;
+      ++i;
+    }
+    if (bp.n == 0)
+      continue;
+    const int st = x_bf16 ? launch_batch<false>(bp, static_cast<int>(tiles), s) : launch_batch<true>(bp, static_cast<int>(tiles), s);
+    if (st != MXB200_OK)
+      return st;
+  }
+  return MXB200_OK;
+}
+
 }  // namespace
 
 }  // namespace mxb200
+
+extern "C" int mxb200_quantize_mx_batch(const mxb200_quantize_job* jobs, int n_jobs, int x_bf16, int scale_rule,
+                                        void* stream) {
+  return mxb200::quantize_batch(jobs, n_jobs, x_bf16 != 0, scale_rule, stream);
+}
 
 extern "C" int mxb200_quantize_mx(const void* x, int x_bf16, int64_t rows, int64_t cols, mxb200_mx_out out,
                                   mxb200_mx_out out_t, int prologue, int scale_rule, void* stream) {

@@ -32,6 +32,7 @@ class StepConfig:
     tokens: int = 16384          # per rank: batch 8 x sequence 2048
     chunk_rows: int = 2048       # lm_head row chunk
     fused_mlp: bool = True       # relu^2 / relu^2-backward quantization inside the fc / proj-dgrad GEMM epilogues
+    batched_weights: bool = True  # the step's weight quantization as a few batched launches instead of one per matrix
 
     @property
     def linear_shapes(self):
@@ -208,10 +209,21 @@ class DpStep:
 
     def quantize_weights(self):
         """Once per optimizer step (the reference's weight cache, fp8.cpp:516-536): fp32 masters -> both layouts."""
-        for ws, qs in zip(self.weights, self.wq):
-            for w, q in zip(ws, qs):
-                self._quant(w, q)
-        self._quant(self.w_lm, self.wq_lm)
+        if not self.cfg.batched_weights:
+            for ws, qs in zip(self.weights, self.wq):
+                for w, q in zip(ws, qs):
+                    self._quant(w, q)
+            self._quant(self.w_lm, self.wq_lm)
+            return
+        # all of them in a few launches: a launch per weight matrix (one or two waves of tiles) is bound by its own
+        # ramp-up and tail
+        jobs = [(w, *nc.mx_outs(q)) for ws, qs in zip(self.weights, self.wq) for w, q in zip(ws, qs)]
+        jobs.append((self.w_lm, *nc.mx_outs(self.wq_lm)))
+        if self.qhook:
+            self.qhook(True)
+        nc.quantize_mx_batch_into(jobs)
+        if self.qhook:
+            self.qhook(False)
 
     def layer_forward(self, l: int, s: int):
         wq = self.wq[l]

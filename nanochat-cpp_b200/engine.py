@@ -18,7 +18,7 @@ from .capi import MxOut, check, lib
 
 __all__ = [
     "Fp8Tensor", "Fp8WeightCache", "MxGemmBackend", "set_mx_gemm_backend", "mx_gemm_backend", "mx_fits",
-    "empty_mx", "empty_mx_scale", "mx_out", "mx_outs", "quantize_mx", "quantize_mx_into",
+    "empty_mx", "empty_mx_scale", "mx_out", "mx_outs", "quantize_mx", "quantize_mx_into", "quantize_mx_batch_into",
     "quantize_mx_relu_square_bwd", "residual_norm_mx", "residual_norm_mx_fits", "quantize_fp8_weight", "mx_qkv_weights", "mx_gemm", "mx_gemm_out",
     "mx_gemm_f32", "mx_gemm_relu_square", "mx_gemm_relu_square_bwd", "mx_grad_direct", "mx_grad_weights", "fp8_matmul", "fp8_qkv", "fp8_relu_square_mlp", "relu_square_mlp_mx", "fp8_eligible",
     "softcap_ce_loss", "softcap_ce_grad_mx", "softcap_cross_entropy",
@@ -125,6 +125,24 @@ def quantize_mx_into(x: torch.Tensor, relu_square: bool, out: MxOut, out_t: MxOu
     check(lib.mxb200_quantize_mx(x.data_ptr(), int(x.dtype == torch.bfloat16), x.size(0), x.size(1), out, out_t,
                                  capi.PROLOGUE_RELU_SQUARE if relu_square else capi.PROLOGUE_NONE, scale_rule,
                                  _stream()), "quantize_mx")
+
+
+def quantize_mx_batch_into(jobs: Sequence[tuple], scale_rule: int = SCALE_REFERENCE) -> None:
+    """quantize_mx_into(x, False, out, out_t) for every (x, out, out_t) of jobs, all bf16 or all fp32, in as few
+    launches as possible: the same bytes as one call each. For runs of small tensors, e.g. the parts of the merged
+    q/k/v weight (src/nanochat/model/fp8/fp8.cpp:155-171) or a model's weights after an optimizer step."""
+    if not jobs:
+        return
+    x0 = jobs[0][0]
+    _require_cuda(x0, "quantize_mx_batch")
+    arr = (capi.QuantizeJob * len(jobs))()
+    for i, (x, out, out_t) in enumerate(jobs):
+        if not (x.is_cuda and x.dim() == 2 and x.is_contiguous() and mx_fits(x.size(0), x.size(1))
+                and x.dtype == x0.dtype and x.dtype in (torch.bfloat16, torch.float32) and x.device == x0.device):
+            raise RuntimeError("MX: expected aligned, contiguous 2D tensors of one dtype with dims % 128")
+        arr[i] = capi.QuantizeJob(x.data_ptr(), x.size(0), x.size(1), out, out_t)
+    check(lib.mxb200_quantize_mx_batch(arr, len(jobs), int(x0.dtype == torch.bfloat16), scale_rule, _stream()),
+          "quantize_mx_batch")
 
 
 def quantize_mx(x: torch.Tensor, rows: bool = True, cols: bool = True, relu_square: bool = False,
@@ -240,12 +258,17 @@ def mx_qkv_weights(wq: torch.Tensor, wk: torch.Tensor, wv: torch.Tensor, cache: 
     def make():
         out = [torch.empty((n, C), dtype=E4M3, device=wq.device), torch.empty((C, n), dtype=E4M3, device=wq.device),
                empty_mx_scale(n, C, wq.device), empty_mx_scale(C, n, wq.device)]
-        row = 0
+        row, jobs = 0, []
         for w in (wq, wk, wv):
             if w.size(1) != C:
                 raise RuntimeError("q/k/v weights must share the input dim")
-            quantize_mx_into(w.detach().contiguous(), False, mx_out(out[0], out[2], row, 0), mx_out(out[1], out[3], 0, row))
+            jobs.append((w.detach().contiguous(), mx_out(out[0], out[2], row, 0), mx_out(out[1], out[3], 0, row)))
             row += w.size(0)
+        if len({j[0].dtype for j in jobs}) == 1:
+            quantize_mx_batch_into(jobs)  # the three parts in one launch
+        else:
+            for x, o, o_t in jobs:
+                quantize_mx_into(x, False, o, o_t)
         return out
     return cache.get(1, [wq, wk, wv], make) if cache is not None else make()
 

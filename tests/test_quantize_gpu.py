@@ -144,3 +144,45 @@ def test_full_size_roundtrip_property():
     et = q.inv_scale_t.view(torch.uint8).view(12, 128, 32, 4, 4).permute(0, 3, 2, 1, 4).reshape(1536, 512).float()
     deqt = (q.data_t.float().view(1536, 512, 32) * torch.exp2(et - 127).unsqueeze(-1)).view(1536, 16384)
     assert (deqt.t() - x.float()).norm() / x.float().norm() < 0.04
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_batch_equals_separate_calls(dtype):
+    """mxb200_quantize_mx_batch: 40 tensors of mixed shapes (more than one launch holds), some into sub-views of a
+    larger buffer as the merged q/k/v weight is built (src/nanochat/model/fp8/fp8.cpp:155-171), one rows-only, one
+    cols-only: the same bytes as a call per tensor."""
+    g = torch.Generator().manual_seed(12)
+    shapes = [(128, 128), (256, 384), (384, 128), (128, 512)] * 10
+    xs = [(torch.randn(r, c, generator=g) * (1 + i)).to(dtype).cuda() for i, (r, c) in enumerate(shapes)]
+    xs[3][5, 7] = float("nan")
+    want = [nc.quantize_mx(x) for x in xs]
+    got = [nc.empty_mx(x.size(0), x.size(1), x.device) for x in xs]
+    jobs = [(x, *nc.mx_outs(q)) for x, q in zip(xs, got)]
+    none = nc.capi.MxOut(None, 0, None, 0)
+    jobs[1] = (xs[1], jobs[1][1], none)   # rows only
+    jobs[2] = (xs[2], none, jobs[2][2])   # columns only
+    nc.quantize_mx_batch_into(jobs)
+    for i, (q, w) in enumerate(zip(got, want)):
+        if i != 2:
+            assert torch.equal(q.data.view(torch.uint8), w.data.view(torch.uint8)), i
+            assert torch.equal(q.inv_scale.view(torch.uint8), w.inv_scale.view(torch.uint8)), i
+        if i != 1:
+            assert torch.equal(q.data_t.view(torch.uint8), w.data_t.view(torch.uint8)), i
+            assert torch.equal(q.inv_scale_t.view(torch.uint8), w.inv_scale_t.view(torch.uint8)), i
+    # merged q/k/v: three parts into row ranges of one buffer == the concatenation quantized at once
+    parts = [torch.randn(r, 256, generator=g).to(dtype).cuda() for r in (256, 128, 128)]
+    merged = nc.mx_qkv_weights(*parts)
+    whole = nc.quantize_mx(torch.cat(parts, 0))
+    for a, b in zip(merged, (whole.data, whole.data_t, whole.inv_scale, whole.inv_scale_t)):
+        assert torch.equal(a.view(torch.uint8), b.view(torch.uint8))
+
+
+def test_batch_rejects_bad_jobs():
+    x = torch.zeros(128, 128, dtype=torch.bfloat16, device="cuda")
+    q = nc.empty_mx(128, 128, x.device)
+    out, out_t = nc.mx_outs(q)
+    with pytest.raises(RuntimeError):
+        nc.quantize_mx_batch_into([(x, out, out_t), (x.float(), out, out_t)])  # mixed dtypes
+    with pytest.raises(RuntimeError):
+        nc.quantize_mx_batch_into([(x[:, :64], out, out_t)])
+    nc.quantize_mx_batch_into([])  # nothing to do
