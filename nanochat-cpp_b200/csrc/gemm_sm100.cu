@@ -1629,8 +1629,9 @@ extern "C" int mxb200_gemm_splits(int64_t M, int64_t N, int64_t K) {
   const int64_t k_tiles = K / 128;
   // Splitting K costs a round trip of fp32 partial tiles through the workspace plus a serial reduction, and on
   // the d12-d26 shapes a narrower tile that fills a wave beat every split measured. It is kept for shapes that
-  // cannot fill even half the machine with tiles alone and have a deep K to share out.
-  if (tiles * 2 > slots)
+  // cannot fill even a quarter of the machine with tiles alone and have a deep K to share out (d12's 768 x 768
+  // weight gradient: 40 us with four splits against 47 us; with half the machine filled a split already loses).
+  if (tiles * 4 > slots)
     return 1;
   int best = 1;
   for (int s = 2; s <= 4; s *= 2) {
