@@ -165,23 +165,26 @@ def run_gpu_arm(args):
         dist.init_process_group("nccl", device_id=device)
 
     cfg = StepConfig()
-    gemm_events = []
+    gemm_events, quant_events = [], []
     collect = [False]
+    last_end = [None]
 
-    def hook(begin: bool):
-        if collect[0]:
-            ev = torch.cuda.Event(enable_timing=True)
-            ev.record()
-            gemm_events.append(ev)
+    def make_hook(store):
+        # One event per launch boundary: the event that ends a launch doubles as the start of the next one (the step's
+        # launches follow each other on one stream), which halves what the instrumentation adds to the stream.
+        def h(begin: bool):
+            if not collect[0]:
+                return
+            if begin and last_end[0] is not None:
+                ev = last_end[0]
+            else:
+                ev = torch.cuda.Event(enable_timing=True)
+                ev.record()
+            store.append(ev)
+            last_end[0] = None if begin else ev
+        return h
 
-    quant_events = []
-
-    def qhook(begin: bool):
-        if collect[0]:
-            ev = torch.cuda.Event(enable_timing=True)
-            ev.record()
-            quant_events.append(ev)
-
+    hook, qhook = make_hook(gemm_events), make_hook(quant_events)
     step = DpStep(cfg, device, rank, world, gemm_hook=hook, quant_hook=qhook)
     flops = cfg.flops_per_step()
 
@@ -190,8 +193,8 @@ def run_gpu_arm(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    # ---- device-resident timing: the timed region carries no per-launch events (two event records per launch cost
-    # about 4 us of stream time each, 5% of a step)
+    # ---- device-resident timing: the timed region carries no per-launch events (an event record per launch boundary
+    # costs a few percent of a step)
     for i in range(args.warmup):
         step.run_step(i)
     barrier()
