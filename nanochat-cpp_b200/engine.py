@@ -475,9 +475,9 @@ class _MxQkv(torch.autograd.Function):
     gradients along their columns (src/nanochat/model/fp8/fp8.cpp:424-462)."""
 
     @staticmethod
-    def forward(ctx, x, wq, wk, wv, gate_cols, cache):
+    def forward(ctx, x, wq, wk, wv, gate_cols, cache, x_mx):
         sizes = (wq.size(0), wk.size(0), wv.size(0))
-        xq = quantize_mx(x)
+        xq = x_mx if x_mx is not None else quantize_mx(x)
         w, w_t, w_scale, w_scale_t = mx_qkv_weights(wq, wk, wv, cache)
         qkv = mx_gemm(xq.data, xq.inv_scale, w, w_scale, torch.bfloat16)
         ctx.save_for_backward(xq.data_t, xq.inv_scale_t, w_t, w_scale_t)
@@ -507,26 +507,30 @@ class _MxQkv(torch.autograd.Function):
             dx.narrow(1, 0, ctx.gate_cols).add_(grads[3])
         if ctx.direct:
             mx_grad_weights(g_t, g_scale_t, x_t, x_scale_t, list(ctx.ws))
-            return dx, None, None, None, None, None
+            return dx, None, None, None, None, None, None
         dw = mx_gemm(g_t, g_scale_t, x_t, x_scale_t, torch.float32)
         parts, row = [], 0
         for w, rows in zip(ctx.ws, sizes):
             parts.append(dw.narrow(0, row, rows).to(w.dtype))
             row += rows
-        return (dx, *parts, None, None)
+        return (dx, *parts, None, None, None)
 
 
 def fp8_qkv(x_2d: torch.Tensor, wq: torch.Tensor, wk: torch.Tensor, wv: torch.Tensor, gate_cols: int = 0,
-            cache: Optional[Fp8WeightCache] = None):
+            cache: Optional[Fp8WeightCache] = None, x_mx: Optional[Fp8Tensor] = None):
     """Attention's c_q, c_k, c_v as fp8_matmuls of the same x_2d (N, in) bf16, merged
     (src/nanochat/model/fp8/fp8.h:58-66, MX branch). Returns (q, k, v), views of one (N, q + k + v) buffer, plus
     x_2d[:, :gate_cols] when gate_cols > 0 (the value-embedding gate's input; its gradient is added to dx in the
-    same pass)."""
+    same pass). x_mx: x_2d already quantized in both layouts (residual_norm_mx), as the reference's attention path
+    takes it (src/nanochat/model/attention/mx_attention.h:20, mx_attention.cpp:45); x_2d then carries autograd and the
+    gate's columns only."""
     n = wq.size(0) + wk.size(0) + wv.size(0)
     if not (mx_fits(x_2d.size(0), x_2d.size(1)) and n % 128 == 0 and all(w.size(0) % 128 == 0 for w in (wq, wk, wv))
             and 0 <= gate_cols <= x_2d.size(1)):
         raise RuntimeError("fp8_qkv: MX needs N, in and every weight's rows % 128")
-    return _MxQkv.apply(x_2d.contiguous(), wq, wk, wv, gate_cols, cache)
+    if x_mx is not None and (x_mx.data is None or x_mx.data_t is None):
+        raise RuntimeError("fp8_qkv: x_mx needs both layouts")
+    return _MxQkv.apply(x_2d.contiguous(), wq, wk, wv, gate_cols, cache, x_mx)
 
 
 class _Fp8ReluSquareMlp(torch.autograd.Function):

@@ -119,6 +119,21 @@ def test_relu_square_mlp_takes_prequantized_input():
     assert torch.equal(y, y2)
 
 
+def test_qkv_takes_prequantized_input():
+    """x_mx from the residual step feeds the merged q/k/v GEMM directly (mx_attention.cpp:45); the gate's columns come
+    from the bf16 n the same kernel writes."""
+    N, C, gate_cols = 256, 256, 16
+    g = torch.Generator(device="cuda").manual_seed(8)
+    x = torch.randn(N, C, device="cuda", generator=g).to(torch.bfloat16)
+    r = torch.randn(N, C, device="cuda", generator=g).to(torch.bfloat16)
+    ws = [(torch.randn(128, C, device="cuda", generator=g) * 0.05).requires_grad_() for _ in range(3)]
+    res, n, n_mx, rstd, s = nc.residual_norm_mx(x, r, gate_cols=gate_cols)
+    full = nc.residual_norm_mx(x, r, gate_cols=C)[1]
+    a = nc.fp8_qkv(n, *ws, gate_cols=gate_cols, x_mx=n_mx)
+    b = nc.fp8_qkv(full, *ws, gate_cols=gate_cols)
+    assert all(torch.equal(u, v) for u, v in zip(a, b))
+
+
 def test_shape_errors():
     x = torch.zeros(128, 192, dtype=torch.bfloat16, device="cuda")
     w = torch.zeros(128, 192, device="cuda")
