@@ -209,6 +209,12 @@ MXB200_API const char* mxb200_strerror(int status);
  * Synchronises the device. */
 MXB200_API int mxb200_device_status(uint32_t* word);
 
+/* Exercises that path without a stuck kernel: launches one warp that waits, with the given limit, on a barrier nothing
+ * will ever arrive on, records the give-up as the kernels do (site 0x7f) and returns normally. The next
+ * mxb200_device_status then reports MXB200_ERR_WATCHDOG once. limit_ns: 1 to 10 000 000 (10 ms). No reference
+ * counterpart: it is how the bounded waits and their reporting are tested. */
+MXB200_API int mxb200_selftest_bounded_wait(uint64_t limit_ns, void* stream);
+
 /* Tuning knobs for measurement, process-wide. tile_n: 128 or 256 = the one-CTA kernel with 128 x tile_n tiles;
  * 384 / 512 = the CTA-pair kernel (256 x 192 / 256 x 256 tile over two SMs); 0 = choose per shape. max_ctas: CTAs of the persistent
  * grid (0 = one per SM). Not part of the reference interface. */

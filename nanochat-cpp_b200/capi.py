@@ -25,7 +25,7 @@ SYMBOLS = (
     "mxb200_softcap_ce_loss", "mxb200_softcap_ce_grad_mx",
     "mxb200_gemm_splits", "mxb200_gemm_workspace_bytes", "mxb200_gemm_splitk", "mxb200_gemm_splitk_static",
     "mxb200_strerror",
-    "mxb200_device_status", "mxb200_set_gemm_config", "mxb200_launch_count", "mxb200_version",
+    "mxb200_device_status", "mxb200_selftest_bounded_wait", "mxb200_set_gemm_config", "mxb200_launch_count", "mxb200_version",
 )
 
 
@@ -77,6 +77,7 @@ def _load() -> ctypes.CDLL:
     lib.mxb200_gemm_workspace_bytes.restype = ctypes.c_size_t
     lib.mxb200_gemm_splitk.argtypes = [vp, vp, vp, vp, vp, i32, vp, i64, i64, i64, vp, i32, i32, vp, ctypes.c_size_t, vp]
     lib.mxb200_gemm_splitk_static.argtypes = [vp, vp, vp, vp, vp, i32, vp, i64, i64, i64, vp, i32, i32, vp]
+    lib.mxb200_selftest_bounded_wait.argtypes = [ctypes.c_uint64, vp]
     lib.mxb200_strerror.argtypes = [i32]
     lib.mxb200_strerror.restype = ctypes.c_char_p
     lib.mxb200_device_status.argtypes = [ctypes.POINTER(ctypes.c_uint32)]

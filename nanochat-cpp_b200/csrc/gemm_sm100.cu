@@ -1666,6 +1666,43 @@ extern "C" int mxb200_set_gemm_config(int tile_n, int max_ctas) {
   return MXB200_OK;
 }
 
+namespace mxb200 {
+namespace {
+
+// One warp, one barrier that nobody arrives on: the same bounded wait as the GEMM's, with a caller-given limit.
+__global__ void mxb200_selftest_wait_kernel(uint64_t limit_ns) {
+  __shared__ uint64_t bar;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    fence_mbar_init();
+  }
+  __syncwarp();
+  const uint64_t t0 = global_timer_ns();
+  bool gave_up = false;
+  while (!mbar_try_wait(&bar, 0)) {
+    if (global_timer_ns() - t0 > limit_ns) {
+      gave_up = true;
+      break;
+    }
+  }
+  if (gave_up && threadIdx.x == 0)
+    atomicCAS(&g_watchdog_word, 0u, 0x80000000u | 0x7fu);
+}
+
+}  // namespace
+}  // namespace mxb200
+
+extern "C" int mxb200_selftest_bounded_wait(uint64_t limit_ns, void* stream) {
+  mxb200::DeviceInfo dev;
+  if (int s = mxb200::current_device(&dev); s != MXB200_OK)
+    return s;
+  if (limit_ns == 0 || limit_ns > 10000000ull)
+    return MXB200_ERR_ARGUMENT;
+  mxb200::mxb200_selftest_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(limit_ns);
+  mxb200::g_launches.fetch_add(1, std::memory_order_relaxed);
+  return mxb200::launch_status();
+}
+
 extern "C" int mxb200_device_status(uint32_t* word) {
   uint32_t w = 0;
   if (cudaDeviceSynchronize() != cudaSuccess)

@@ -336,3 +336,21 @@ def test_overlapping_launches_on_two_streams():
     torch.cuda.synchronize()
     assert all(torch.equal(o, want1) for o in outs1)
     assert all(torch.equal(o, want2) for o in outs2)
+
+
+def test_bounded_wait_reports_and_clears():
+    """Every device-side wait gives up after a limit, records where, and the kernel returns: a warp that waits 1 ms on a
+    barrier nothing arrives on comes back, the status call reports it once, and the device goes on working."""
+    lib = nc.capi.lib
+    assert nc.capi.device_status() == 0
+    assert lib.mxb200_selftest_bounded_wait(1_000_000, torch.cuda.current_stream().cuda_stream) == nc.capi.OK
+    import ctypes
+    word = ctypes.c_uint32(0)
+    assert lib.mxb200_device_status(ctypes.byref(word)) == nc.capi.ERR_WATCHDOG
+    assert word.value == 0x8000007F
+    assert lib.mxb200_device_status(ctypes.byref(word)) == nc.capi.OK and word.value == 0
+    assert lib.mxb200_selftest_bounded_wait(0, None) == nc.capi.ERR_ARGUMENT
+    assert lib.mxb200_selftest_bounded_wait(20_000_000, None) == nc.capi.ERR_ARGUMENT
+    qa, qb = quantized(256, 256, 256, seed=31)
+    got = nc.mx_gemm(qa.data, qa.inv_scale, qb.data, qb.inv_scale, torch.float32)
+    assert rel(got.cpu(), oracle_product(qa, qb)) < TOL_F32
