@@ -140,7 +140,10 @@ MXB200_API int mxb200_residual_norm_mx_fwd(const mxb200_residual_norm_mx* args, 
  * fp32 accumulation, one round-to-nearest-even to bf16. M, N, K % 128 == 0, pointers 16-byte aligned.
  * resid (optional, (M, N) bf16): the fused residual add, d = bf16(float(bf16(acc)) + float(resid)), the two
  * roundings of the reference's separate add (src/nanochat/model/ops/residual_norm_kernel.cu:96-104).
- * resid may alias d. Needs no workspace. */
+ * resid may alias d. Needs no workspace. Launches on different streams of one device may overlap; at most 1024 GEMM
+ * launches of this library may be in flight on a device at once (each holds one of 1024 scheduler slots in the
+ * library's device image until its kernel exits; the same limit applies to concurrent replays of one CUDA graph,
+ * whose launches keep the slot they were captured with). */
 MXB200_API int mxb200_gemm_bf16(const void* a, const void* a_scale, const void* b, const void* b_scale, void* d, const void* resid,
                      int64_t M, int64_t N, int64_t K, void* stream);
 
@@ -153,7 +156,9 @@ MXB200_API int mxb200_gemm_f32(const void* a, const void* a_scale, const void* b
 /* Replaces nanochat::kernels::cutlass_mx_gemm_relu_square (src/nanochat/model/fp8/mx_gemm_kernel.h:24-27; used by the
  * MLP forward, fp8.cpp:279-284): h (M, N) bf16 = a . b^T as mxb200_gemm_bf16, and in the same epilogue the outputs
  * of mxb200_quantize_mx(h, RELU_SQUARE), bit for bit: q (M, N) e4m3 + q_scale, q_t (N, M) e4m3 + q_t_scale, each
- * a whole contiguous tensor with its own swizzled scale buffer (M * N / 32 bytes). */
+ * a whole contiguous tensor with its own swizzled scale buffer (M * N / 32 bytes). Both fused-quantize GEMMs use
+ * MXB200_SCALE_REFERENCE, the only rule the reference's fused kernels have; MXB200_SCALE_OCP_FLOOR exists in the
+ * stand-alone quantizer only. */
 MXB200_API int mxb200_gemm_relu_square(const void* a, const void* a_scale, const void* b, const void* b_scale, void* h,
                                        void* q, void* q_scale, void* q_t, void* q_t_scale, int64_t M, int64_t N,
                                        int64_t K, void* stream);

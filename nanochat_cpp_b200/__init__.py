@@ -1,8 +1,6 @@
-"""Import shim: the package lives in the directory ``nanochat-cpp_b200`` (not an identifier), this makes it
-importable as ``nanochat_cpp_b200``."""
-import os as _os
+"""mxb200: the MXFP8 Linear path of nanochat-cpp (quantizer, block-scaled GEMM and their callers) on B200.
 
-__path__.insert(0, _os.path.join(_os.path.dirname(_os.path.dirname(_os.path.abspath(__file__))), "nanochat-cpp_b200"))
-
-from .engine import *  # noqa: F401,F403,E402
-from . import capi, engine  # noqa: F401,E402
+``capi`` binds the C-ABI library ``libmxb200.so`` (include/mxb200.h); ``engine`` mirrors the reference's host
+interface (src/nanochat/model/fp8/fp8.h, mx_gemm.h) over it; ``dp_step`` is the data-parallel step."""
+from .engine import *  # noqa: F401,F403
+from . import capi, engine  # noqa: F401

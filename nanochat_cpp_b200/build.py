@@ -1,6 +1,6 @@
 """Builds libmxb200.so (the C-ABI library) in-tree with nvcc for sm_100a.
 
-    python nanochat-cpp_b200/build.py          # rebuild when a source is newer than the library
+    python nanochat_cpp_b200/build.py          # rebuild when a source is newer than the library
 
 nvcc cross-compiles without a GPU. The library links the CUDA runtime statically and takes the one driver
 entry point it needs (cuTensorMapEncodeTiled) through cudaGetDriverEntryPoint, so it has no link-time
@@ -27,6 +27,14 @@ def _nvcc() -> str:
         if cand and os.path.exists(cand):
             return cand
     raise RuntimeError("nvcc not found; libmxb200.so cannot be built")
+
+
+def have_nvcc() -> bool:
+    try:
+        _nvcc()
+        return True
+    except RuntimeError:
+        return False
 
 
 def _stale() -> bool:

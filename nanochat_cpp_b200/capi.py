@@ -56,9 +56,9 @@ class Mxb200Error(RuntimeError):
 
 
 def _load() -> ctypes.CDLL:
-    if not os.path.exists(LIB_PATH):
-        from .build import build
-        build()
+    from .build import build, have_nvcc
+    if not os.path.exists(LIB_PATH) or have_nvcc():
+        build()  # returns at once unless a source is newer than the library: an edited kernel never runs stale
     lib = ctypes.CDLL(LIB_PATH)
     vp, i64, i32 = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int
     lib.mxb200_quantize_mx.argtypes = [vp, i32, i64, i64, MxOut, MxOut, i32, i32, vp]

@@ -43,19 +43,12 @@ __device__ uint32_t g_watchdog_word;
 static __device__ __align__(256) unsigned char g_static_splitk_scratch[MXB200_STATIC_SCRATCH_BYTES];
 
 // Work counters of the CTA-pair kernel's tile scheduler: {next unit, pairs done} per launch slot, zero between
-// launches (the last pair to finish a launch zeroes its slot). Launches take slots round-robin, so kernels that
-// overlap on one device (different streams) do not share one.
-constexpr int kSchedLaunchSlots = 64;
+// launches (the last pair to leave a launch zeroes its slot, whether or not a bounded wait gave up on the way).
+// Launches take slots round-robin, so kernels that overlap on one device (different streams) do not share one as
+// long as fewer than kSchedLaunchSlots pair launches are in flight on the device at once.
+constexpr int kSchedLaunchSlots = 1024;
 __device__ uint32_t g_sched_words[2 * kSchedLaunchSlots];
 
-#ifdef MXB200_TRACE
-// Development aid (never compiled into the shipped library): per-tile timestamps of the first CTA pair.
-__device__ unsigned long long g_trace[8192];
-#define TRACE(slot, idx) \
-  do { if (blockIdx.x == 0 && (idx) < 64) g_trace[(slot) * 64 + (idx)] = clock64(); } while (0)
-#else
-#define TRACE(slot, idx) do { } while (0)
-#endif
 
 namespace {
 
@@ -1012,7 +1005,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairConfig<TN, kFuse
         const int row_a = tc.m * C::kTileM + static_cast<int>(rank) * 128;
         const int row_b = tc.n * C::kTileN + static_cast<int>(rank) * C::kBRows;
         const int sfa_tile = row_a >> 7, sfb_tile = (tc.n * C::kTileN) >> 7;
-        if (el) TRACE(4, seq);
         for (int kt = k_begin; kt < k_end; ++kt) {
           if (!wait_bounded_warp(empty0 + stage * 8, phase ^ 1u, bars, kSiteProducerEmpty)) {
             ok = false;
@@ -1034,8 +1026,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairConfig<TN, kFuse
           drawn = __shfl_sync(0xffffffffu, drawn, 0);
       }
       // the launch's last pair leaves the counters at zero for the next launch that takes this slot; every pair's
-      // final draw (the one past the end) has happened before it counts itself done
-      if (leader && ok && lane == 0 && atomicAdd(&sched[1], 1u) == static_cast<uint32_t>(num_pairs) - 1u) {
+      // final draw (the one past the end) has happened before it counts itself done. A pair that gave up on a
+      // bounded wait counts itself too: a slot must never stay part-way through a unit list.
+      if (leader && lane == 0 && atomicAdd(&sched[1], 1u) == static_cast<uint32_t>(num_pairs) - 1u) {
         sched[0] = 0;
         sched[1] = 0;
       }
@@ -1076,7 +1069,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairConfig<TN, kFuse
           break;
         }
         tcgen05_fence_after_sync();
-        if (el) TRACE(0, local);
         const uint32_t acc_t = tmem_base + (buf ? C::kAcc1 : C::kAcc0);
         // the tile's first column is ((n * TN) % 128) / 32 scale columns into the first of B's two tiles
         const uint32_t sfb_mma = sfb_t + static_cast<uint32_t>(((tc.n * C::kTileN) & 127) >> 5);
@@ -1110,7 +1102,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairConfig<TN, kFuse
         }
         if (ok)
           tcgen05_commit_pair(el, &bars->tmem_full[buf], 3);
-        if (el) TRACE(1, local);
       }
     }
   } else {
@@ -1158,7 +1149,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairConfig<TN, kFuse
         break;
       }
       tcgen05_fence_after_sync();
-      if (threadIdx.x == 64) TRACE(2, local);
       const uint32_t acc_t = tmem_base + lane_base + (buf ? C::kAcc1 : C::kAcc0);
       const int64_t row = static_cast<int64_t>(tc.m) * C::kTileM + rank * 128 + quarter * 32 + lane;
       const bool row_ok = row < p.M;
@@ -1216,7 +1206,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairConfig<TN, kFuse
       __syncwarp();
       if (lane == 0)
         mbar_arrive_cluster(empty_leader[buf]);
-      if (threadIdx.x == 64) TRACE(3, local);
 
       if (part != nullptr) {
         // split-K, per half tile: the rows of this CTA are reduced by whichever CTA finishes them last
@@ -1751,13 +1740,6 @@ extern "C" int mxb200_gemm_splitk_static(const void* a, const void* a_scale, con
   return mxb200::gemm(a, a_scale, b, b_scale, d, out_kind, resid, M, N, K, alpha, accumulate, splits, scratch,
                       MXB200_STATIC_SCRATCH_BYTES, stream);
 }
-
-#ifdef MXB200_TRACE
-extern "C" __attribute__((visibility("default"))) int mxb200_trace_read(unsigned long long* out, int n) {
-  cudaDeviceSynchronize();
-  return cudaMemcpyFromSymbol(out, mxb200::g_trace, sizeof(unsigned long long) * n) == cudaSuccess ? 0 : 1;
-}
-#endif
 
 extern "C" int mxb200_gemm_relu_square(const void* a, const void* a_scale, const void* b, const void* b_scale, void* h,
                                        void* q, void* q_scale, void* q_t, void* q_t_scale, int64_t M, int64_t N,

@@ -33,6 +33,11 @@ class StepConfig:
     chunk_rows: int = 2048       # lm_head row chunk
     fused_mlp: bool = True       # relu^2 / relu^2-backward quantization inside the fc / proj-dgrad GEMM epilogues
     batched_weights: bool = True  # the step's weight quantization as a few batched launches instead of one per matrix
+    # Weight gradients: False = one bf16 write per matrix straight into the reduce-scatter bucket (a step without
+    # gradient accumulation); True = the reference's default, fp32 `+=` into the weights' .grad buffers
+    # (src/nanochat/model/fp8/fp8.cpp:470-514) followed by the cast of each layer's gradients into the bucket
+    # (src/nanochat/train/optim.cpp:459).
+    wgrad_fp32_accumulate: bool = False
 
     @property
     def linear_shapes(self):
@@ -185,14 +190,61 @@ class DpStep:
         self.dx_lm = torch.empty((M, C), dtype=bf, device=device)
 
         self.bucket = GradBucket(cfg, device, world)
+        # fp32 .grad buffers, only for the accumulate form
+        self.grads = self.grad_lm = None
+        self.set_wgrad_fp32_accumulate(cfg.wgrad_fp32_accumulate)
+        # "b200": this library; "cublaslt": the same GEMMs through torch._scaled_mm, the arithmetic of the
+        # reference's --gemm=cublas (src/nanochat/model/fp8/mx_gemm.cpp:158); gemm_only: replay the GEMMs over the
+        # operands quantized by an earlier step, no quantizer launches
+        self.gemm_impl = "b200"
+        self.gemm_only = False
         self.comm_stream = torch.cuda.Stream(device=device) if (device.type == "cuda" and world > 1) else None
         self._pending: list = []
+
+    def set_wgrad_fp32_accumulate(self, on: bool):
+        """Switches the weight-gradient form (StepConfig.wgrad_fp32_accumulate); the fp32 .grad buffers (4 bytes per
+        parameter) are allocated on first use."""
+        self.cfg.wgrad_fp32_accumulate = on
+        if on and self.grads is None:
+            cfg, device = self.cfg, self.device
+            self.grads = [[torch.zeros((n, k), dtype=torch.float32, device=device) for _, n, k in cfg.linear_shapes]
+                          for _ in range(cfg.n_layer)]
+            self.grad_lm = torch.zeros((cfg.vocab, cfg.n_embd), dtype=torch.float32, device=device)
+
+    def _grad(self, layer: int, index: int):
+        return self.grads[layer][index] if self.cfg.wgrad_fp32_accumulate else None
+
+    def _cast_grads(self, layer: int):
+        """The accumulate form's last step before the collective: fp32 .grad -> the bf16 bucket."""
+        if not self.cfg.wgrad_fp32_accumulate or self.gemm_impl == "cublaslt":
+            return
+        if layer == self.cfg.n_layer:
+            self.bucket.lm_head().copy_(self.grad_lm)
+            return
+        for j in range(4):
+            self.bucket.matrix(layer, j).copy_(self.grads[layer][j])
 
     # ------------------------------------------------------------------ pieces
     def _gemm(self, out, a, a_scale, b, b_scale, resid=None):
         if self.hook:
             self.hook(True)
-        nc.mx_gemm_out(out, a, a_scale, b, b_scale, resid)
+        if self.gemm_impl == "cublaslt":
+            # the library call the reference's cuBLAS backend makes; its residual add is a separate kernel of the
+            # residual step and is left out here (in cuBLASLt's favour)
+            torch._scaled_mm(a, b.t(), a_scale, b_scale, None, None, out.dtype, False, out=out)
+        else:
+            nc.mx_gemm_out(out, a, a_scale, b, b_scale, resid)
+        if self.hook:
+            self.hook(False)
+
+    def _wgrad(self, bucket_view, grad, a, a_scale, b, b_scale):
+        """One weight gradient: bf16 straight into the bucket, or fp32 += into .grad (cast to the bucket later)."""
+        if grad is None or self.gemm_impl == "cublaslt":
+            self._gemm(bucket_view, a, a_scale, b, b_scale)
+            return
+        if self.hook:
+            self.hook(True)
+        nc.mx_gemm_f32(a, a_scale, b, b_scale, grad, True)
         if self.hook:
             self.hook(False)
 
@@ -201,6 +253,8 @@ class DpStep:
         self._quant_into(x, relu_square, out, out_t)
 
     def _quant_into(self, x, relu_square, out, out_t):
+        if self.gemm_only:
+            return
         if self.qhook:
             self.qhook(True)
         nc.quantize_mx_into(x, relu_square, out, out_t)
@@ -209,6 +263,8 @@ class DpStep:
 
     def quantize_weights(self):
         """Once per optimizer step (the reference's weight cache, fp8.cpp:516-536): fp32 masters -> both layouts."""
+        if self.gemm_only:
+            return
         if not self.cfg.batched_weights:
             for ws, qs in zip(self.weights, self.wq):
                 for w, q in zip(ws, qs):
@@ -232,7 +288,7 @@ class DpStep:
         self._quant(self.y_att[s], self.yq_att[l])
         self._gemm(self.out_c, self.yq_att[l].data, self.yq_att[l].inv_scale, wq[1].data, wq[1].inv_scale, self.resid[s])
         self._quant(self.x_mlp[s], self.xq_mlp[l])
-        if self.cfg.fused_mlp:
+        if self.cfg.fused_mlp and not self.gemm_only:
             # fc GEMM writes h and, from the same epilogue, MX(relu(h)^2) in both layouts (fp8.cpp:279-284)
             if self.hook:
                 self.hook(True)
@@ -250,7 +306,7 @@ class DpStep:
         wq, b = self.wq[l], self.bucket
         # MLP proj: dA = dY . W, dW = dY^T . A
         self._quant(self.dy_proj[s], self.gq_c)
-        if self.cfg.fused_mlp:
+        if self.cfg.fused_mlp and not self.gemm_only:
             # dgrad GEMM whose epilogue reads h and emits MX(dh) directly; dA is never written (fp8.cpp:318-323)
             if self.hook:
                 self.hook(True)
@@ -262,24 +318,25 @@ class DpStep:
             self._gemm(self.da, self.gq_c.data, self.gq_c.inv_scale, wq[3].data_t, wq[3].inv_scale_t)
             # relu^2 backward as a prologue of the quantizer: dh = bf16(h > 0 ? dA * 2h : 0)
             out, out_t = nc.mx_outs(self.gq_4c)
-            if self.qhook:
+            if self.qhook and not self.gemm_only:
                 self.qhook(True)
-            nc.check(nc.lib.mxb200_quantize_mx_relu_square_bwd(self.da.data_ptr(), self.h[l].data_ptr(), self.da.size(0),
-                                                               self.da.size(1), out, out_t, nc.SCALE_REFERENCE,
-                                                               torch.cuda.current_stream().cuda_stream), "quantize dh")
-            if self.qhook:
+            if not self.gemm_only:
+                nc.check(nc.lib.mxb200_quantize_mx_relu_square_bwd(
+                    self.da.data_ptr(), self.h[l].data_ptr(), self.da.size(0), self.da.size(1), out, out_t,
+                    nc.SCALE_REFERENCE, torch.cuda.current_stream().cuda_stream), "quantize dh")
+            if self.qhook and not self.gemm_only:
                 self.qhook(False)
-        self._gemm(b.matrix(l, 3), self.gq_c.data_t, self.gq_c.inv_scale_t, self.aq[l].data_t, self.aq[l].inv_scale_t)
+        self._wgrad(b.matrix(l, 3), self._grad(l, 3), self.gq_c.data_t, self.gq_c.inv_scale_t, self.aq[l].data_t, self.aq[l].inv_scale_t)
         self._gemm(self.dx, self.gq_4c.data, self.gq_4c.inv_scale, wq[2].data_t, wq[2].inv_scale_t)
-        self._gemm(b.matrix(l, 2), self.gq_4c.data_t, self.gq_4c.inv_scale_t, self.xq_mlp[l].data_t, self.xq_mlp[l].inv_scale_t)
+        self._wgrad(b.matrix(l, 2), self._grad(l, 2), self.gq_4c.data_t, self.gq_4c.inv_scale_t, self.xq_mlp[l].data_t, self.xq_mlp[l].inv_scale_t)
         # attention out
         self._quant(self.dy_o[s], self.gq_c)
         self._gemm(self.dx, self.gq_c.data, self.gq_c.inv_scale, wq[1].data_t, wq[1].inv_scale_t)
-        self._gemm(b.matrix(l, 1), self.gq_c.data_t, self.gq_c.inv_scale_t, self.yq_att[l].data_t, self.yq_att[l].inv_scale_t)
+        self._wgrad(b.matrix(l, 1), self._grad(l, 1), self.gq_c.data_t, self.gq_c.inv_scale_t, self.yq_att[l].data_t, self.yq_att[l].inv_scale_t)
         # merged QKV
         self._quant(self.dy_qkv[s], self.gq_3c)
         self._gemm(self.dx, self.gq_3c.data, self.gq_3c.inv_scale, wq[0].data_t, wq[0].inv_scale_t)
-        self._gemm(b.matrix(l, 0), self.gq_3c.data_t, self.gq_3c.inv_scale_t, self.xq_attn[l].data_t, self.xq_attn[l].inv_scale_t)
+        self._wgrad(b.matrix(l, 0), self._grad(l, 0), self.gq_3c.data_t, self.gq_3c.inv_scale_t, self.xq_attn[l].data_t, self.xq_attn[l].inv_scale_t)
 
     def lm_head(self):
         """Chunked logits GEMM, gradient quantized per chunk into row/column ranges of one MX buffer, dX per chunk,
@@ -298,17 +355,28 @@ class DpStep:
             ga = self.gq_lm.data[begin:begin + rows]
             gs = self.gq_lm.inv_scale[begin * cfg.vocab // 32:(begin + rows) * cfg.vocab // 32]
             self._gemm(self.dx_lm[begin:begin + rows], ga, gs, self.wq_lm.data_t, self.wq_lm.inv_scale_t)
-        self._gemm(self.bucket.lm_head(), self.gq_lm.data_t, self.gq_lm.inv_scale_t, self.xq_lm.data_t, self.xq_lm.inv_scale_t)
+        self._wgrad(self.bucket.lm_head(), self.grad_lm if self.cfg.wgrad_fp32_accumulate else None, self.gq_lm.data_t,
+                    self.gq_lm.inv_scale_t, self.xq_lm.data_t, self.xq_lm.inv_scale_t)
 
     def _reduce_segment(self, i: int):
         """Reduce-scatter segment i on the communication stream once the compute stream has produced it."""
-        if self.world == 1:
+        if self.world == 1 or self.gemm_only:
             return
         ev = torch.cuda.Event()
         ev.record()
         self.comm_stream.wait_event(ev)
         with torch.cuda.stream(self.comm_stream):
             self._pending.append(self.bucket.reduce_scatter(i, async_op=True))
+
+    def run_gemms_only(self, impl: str = "b200"):
+        """The step's 305 GEMMs again, back to back, over the operands an earlier run_step quantized: no quantizer
+        launches, plain epilogues (the two MLP GEMMs without their fused quantization), no collective. impl
+        "cublaslt" sends the same operands through torch._scaled_mm."""
+        self.gemm_only, self.gemm_impl = True, impl
+        try:
+            self.run_step(0)
+        finally:
+            self.gemm_only, self.gemm_impl = False, "b200"
 
     def finish_collectives(self):
         for w in self._pending:
@@ -326,8 +394,10 @@ class DpStep:
         for l in range(cfg.n_layer):
             self.layer_forward(l, (step + l) % n_sets)
         self.lm_head()
+        self._cast_grads(cfg.n_layer)
         self._reduce_segment(cfg.n_layer)
         for l in reversed(range(cfg.n_layer)):
             self.layer_backward(l, (step + l) % n_sets)
+            self._cast_grads(l)
             self._reduce_segment(l)
         self.finish_collectives()

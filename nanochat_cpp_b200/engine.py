@@ -279,9 +279,13 @@ _workspaces: dict = {}
 
 
 def _workspace(device, nbytes: int) -> torch.Tensor:
-    """Split-K scratch, grown on demand and kept per device (the reference's cuBLASLt path likewise borrows
-    torch's workspace, src/nanochat/model/fp8/mx_gemm.cpp:236-237)."""
-    key = (device.type, device.index if device.index is not None else torch.cuda.current_device())
+    """Split-K scratch, grown on demand and kept per (device, stream): split-K GEMMs on different streams may
+    overlap on the GPU and must not share partial tiles and counters, while launches on one stream are ordered
+    and reuse theirs (the reference's cuBLASLt path likewise borrows torch's per-stream workspace,
+    src/nanochat/model/fp8/mx_gemm.cpp:236-237). A replaced tensor is handed back to the caching allocator, which
+    keeps it for the stream it was allocated on until that stream's queued work has run."""
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    key = (index, torch.cuda.current_stream(index).cuda_stream)
     ws = _workspaces.get(key)
     if ws is None or ws.numel() < nbytes:
         ws = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)

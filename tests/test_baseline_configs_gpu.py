@@ -75,7 +75,8 @@ def test_config2_d24_forward_set(name, N, K, resid):
     assert rel(np_f32(y)[ROWS], want) < TOL_BF16
 
 
-@pytest.mark.parametrize("name,N,K", [("qkv", 4608, 1536), ("mlp_proj", 1536, 6144)])
+@pytest.mark.parametrize("name,N,K", [("qkv", 4608, 1536), ("attn_out", 1536, 1536), ("mlp_fc", 6144, 1536),
+                                      ("mlp_proj", 1536, 6144)])
 def test_config3_d24_backward_set(name, N, K):
     """dY bf16 [16384, N] ~ N(0, 1e-3): dgrad dX = dYq . (W_t)^T and wgrad dW = (dY_t)q . (X_t)q^T with the scales along
     the 16384 tokens; bf16 into the bucket and fp32 accumulation."""
@@ -137,3 +138,91 @@ def test_config4_lm_head_chunks_student_t():
         da = mo.mx_dequantize(np_u8(qx.data), np_u8(qx.inv_scale))[begin + rows]
         db = mo.mx_dequantize(np_u8(qw.data), np_u8(qw.inv_scale))
         assert rel(np_f32(logits)[rows], da @ db.T) < TOL_BF16, c
+
+
+def student_t_activations(g, M, C):
+    z = torch.randn(M, C, device="cuda", generator=g)
+    chi2 = torch.randn(M, C, 3, device="cuda", generator=g).square().sum(-1)
+    return (0.5 * z / (chi2 / 3).sqrt()).to(torch.bfloat16)
+
+
+def test_config4_lm_head_backward_chunks():
+    """The other two GEMMs of the chunked lm_head (src/nanochat/model/ops/softcap_ce.cpp:88, 109): per chunk of 2048
+    tokens dX = gq . (W_t)^T with K = the 32768-entry vocabulary, and once over all chunks dW = (g_t)q . (X_t)q^T with
+    K = 16384 tokens, the gradient's transposed layout written chunk by chunk into one (vocab, tokens) buffer.
+    dlogits ~ N(0, 1e-3) bf16; sampled rows against the oracle's dequantized products."""
+    M, C, V, chunk = 16384, 1536, 32768, 2048
+    g = torch.Generator(device="cuda").manual_seed(5)
+    x = student_t_activations(g, M, C)
+    w = (torch.randn(V, C, device="cuda", generator=g) / C ** 0.5).to(torch.bfloat16)
+    qx, qw = nc.quantize_mx(x, False, True), nc.quantize_mx(w, False, True)
+    g_all = nc.empty_mx(M, V, x.device, rows=False)  # only the (vocab, tokens) layout is kept across chunks
+    dw_t = mo.mx_dequantize(np_u8(qw.data_t), np_u8(qw.inv_scale_t))  # [C, V]
+    rows = np.array([0, 777, 2047])
+    for c in range(M // chunk):
+        begin = c * chunk
+        dl = (torch.randn(chunk, V, device="cuda", generator=g) * 1e-3).to(torch.bfloat16)
+        gq = nc.empty_mx(chunk, V, x.device, cols=False)
+        nc.quantize_mx_into(dl, False, nc.mx_out(gq.data, gq.inv_scale),
+                            nc.mx_out(g_all.data_t, g_all.inv_scale_t, 0, begin))
+        if c in (0, 5):
+            og = mo.quantize_mx(np_f32(dl[:, 4096:4224]), False, True)
+            assert np.array_equal(np_u8(g_all.data_t[4096:4224, begin:begin + chunk]), og["data_t"])
+            dx = nc.mx_gemm(gq.data, gq.inv_scale, qw.data_t, qw.inv_scale_t, torch.bfloat16)  # [2048, 1536], K = 32768
+            da = mo.mx_dequantize(np_u8(gq.data), np_u8(gq.inv_scale))[rows]
+            assert rel(np_f32(dx)[rows], da @ dw_t.T) < TOL_BF16, c
+        del dl, gq
+    # the one weight-gradient GEMM over all tokens: [V, C] = g_t [V, M] . X_t [C, M]^T
+    dw = torch.zeros(V, C, dtype=torch.float32, device="cuda")
+    nc.mx_gemm_f32(g_all.data_t, g_all.inv_scale_t, qx.data_t, qx.inv_scale_t, dw, False)
+    dx_t = mo.mx_dequantize(np_u8(qx.data_t), np_u8(qx.inv_scale_t)).astype(np.float64)
+    per_row_tile = (M // 128) * 512  # scale bytes of one 128-row tile of the (vocab, tokens) layout
+    for rt, inside in ((0, [0, 127]), (157, [1, 64]), (V // 128 - 1, [126, 127])):
+        slab = slice(rt * 128, rt * 128 + 128)
+        dg_t = mo.mx_dequantize(np_u8(g_all.data_t[slab]),
+                                np_u8(g_all.inv_scale_t[rt * per_row_tile:(rt + 1) * per_row_tile]))[inside]
+        want = dg_t.astype(np.float64) @ dx_t.T
+        got = np_f32(dw[slab])[inside]
+        assert rel(got, want) < TOL_F32 * 3, rt  # 16384 terms: fp32 accumulation order
+    dw16 = nc.mx_gemm(g_all.data_t, g_all.inv_scale_t, qx.data_t, qx.inv_scale_t, torch.bfloat16)
+    assert torch.equal(dw16, dw.to(torch.bfloat16))
+    alpha = torch.tensor([0.125], device="cuda")
+    first = dw.clone()
+    nc.mx_gemm_f32(g_all.data_t, g_all.inv_scale_t, qx.data_t, qx.inv_scale_t, dw, True, alpha=alpha)
+    assert torch.equal(dw, first * 1.125)  # += alpha . product, alpha a power of two: exact
+
+
+def test_fused_quantize_epilogues_at_d24_size():
+    """The two GEMMs of the relu^2 MLP that quantize in their epilogue (src/nanochat/model/fp8/fp8.cpp:279-284,
+    318-323), at the d24 step's own size 16384 x 6144 x 1536: h and MX(relu(h)^2), and MX(dh) from ga and h, equal
+    the GEMM followed by the stand-alone quantizer bit for bit (tests/test_fp8.cpp:363-426 at small sizes)."""
+    M, N, K = 16384, 6144, 1536
+    g = torch.Generator(device="cuda").manual_seed(6)
+    x = torch.randn(M, K, device="cuda", generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, device="cuda", generator=g) / K ** 0.5).to(torch.bfloat16)
+    qx, qw = nc.quantize_mx(x, True, False), nc.quantize_mx(w, True, False)
+    want_h = nc.mx_gemm(qx.data, qx.inv_scale, qw.data, qw.inv_scale, torch.bfloat16)
+    want = nc.quantize_mx(want_h, True, True, True)
+    h = torch.full_like(want_h, float("nan"))
+    got = nc.empty_mx(M, N, x.device)
+    for t in (got.data, got.data_t, got.inv_scale, got.inv_scale_t):
+        t.view(torch.uint8).zero_()
+    assert nc.mx_gemm_relu_square(h, got.data, got.inv_scale, got.data_t, got.inv_scale_t, qx.data, qx.inv_scale,
+                                  qw.data, qw.inv_scale)
+    assert torch.equal(h, want_h)
+    for name in ("data", "inv_scale", "data_t", "inv_scale_t"):
+        a, b = getattr(got, name).view(torch.uint8), getattr(want, name).view(torch.uint8)
+        assert torch.equal(a, b), f"relu^2 {name}: {(a != b).sum().item()} bytes differ"
+    # a slab of the fused output against the CPU oracle's relu^2 prologue
+    slab = slice(8192, 8192 + 128)
+    ref = mo.quantize_mx(np_f32(want_h[slab, :256]), True, False, mo.PROLOGUE_RELU_SQUARE)
+    assert np.array_equal(np_u8(got.data[slab, :256]), ref["data"])
+    # backward form: ga = dYq . (W_proj_t)^T with the same operand shapes, h the forward's output
+    want_bwd = nc.quantize_mx_relu_square_bwd(want_h, h)  # ga := want_h as a stand-in gradient of the same shape
+    for t in (got.data, got.data_t, got.inv_scale, got.inv_scale_t):
+        t.view(torch.uint8).zero_()
+    assert nc.mx_gemm_relu_square_bwd(qx.data, qx.inv_scale, qw.data, qw.inv_scale, h, got.data, got.inv_scale,
+                                      got.data_t, got.inv_scale_t)
+    for name in ("data", "inv_scale", "data_t", "inv_scale_t"):
+        a, b = getattr(got, name).view(torch.uint8), getattr(want_bwd, name).view(torch.uint8)
+        assert torch.equal(a, b), f"relu^2 bwd {name}: {(a != b).sum().item()} bytes differ"

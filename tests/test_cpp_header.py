@@ -45,7 +45,7 @@ def test_header_compiles_links_and_reports_errors(tmp_path):
     if not os.path.exists(os.path.join(cuda_inc, "cuda_runtime_api.h")):
         pytest.skip("CUDA runtime headers not found")
     import nanochat_cpp_b200  # builds the library if needed  # noqa: F401
-    lib_dir = os.path.join(ROOT, "nanochat-cpp_b200")
+    lib_dir = os.path.join(ROOT, "nanochat_cpp_b200")
     src = tmp_path / "seam.cpp"
     src.write_text(PROGRAM)
     exe = tmp_path / "seam"

@@ -354,3 +354,20 @@ def test_bounded_wait_reports_and_clears():
     qa, qb = quantized(256, 256, 256, seed=31)
     got = nc.mx_gemm(qa.data, qa.inv_scale, qb.data, qb.inv_scale, torch.float32)
     assert rel(got.cpu(), oracle_product(qa, qb)) < TOL_F32
+
+
+def test_gemm_after_an_unreported_give_up():
+    """A bounded wait that ran out and was never read back with mxb200_device_status must not disturb the launches
+    that follow: the scheduler counters of a launch are left at zero by its last pair whether or not a wait gave up,
+    so GEMMs of several shapes right after a give-up still match the oracle. The status word is read (and cleared)
+    only at the end."""
+    lib = nc.capi.lib
+    assert nc.capi.device_status() == 0
+    assert lib.mxb200_selftest_bounded_wait(500_000, torch.cuda.current_stream().cuda_stream) == nc.capi.OK
+    for M, N, K, seed in ((512, 768, 256, 41), (1024, 1280, 512, 42), (256, 256, 1024, 43)):
+        qa, qb = quantized(M, N, K, seed=seed)
+        for _ in range(3):
+            got = nc.mx_gemm(qa.data, qa.inv_scale, qb.data, qb.inv_scale, torch.float32)
+        assert rel(got.cpu(), oracle_product(qa, qb)) < TOL_F32
+    assert nc.capi.device_status() == 0x8000007F  # the give-up is still reported, once
+    assert nc.capi.device_status() == 0

@@ -85,3 +85,23 @@ def test_static_scratch_refuses_what_does_not_fit():
                                                torch.cuda.current_stream().cuda_stream)
     assert st == nc.capi.ERR_WORKSPACE
     assert "workspace" in nc.capi.strerror(st)
+
+
+def test_static_scratch_calls_take_no_device_memory():
+    """What the entry point is for: across its calls the device's free memory does not move (no cudaMalloc by the
+    library, the runtime or an allocator on its behalf). Outputs are allocated beforehand; the first call on the
+    device, which looks up the array's address, is made before the measurement."""
+    M, N, K = 512, 768, 4096
+    qa, qb = _operands(M, N, K, seed=34)
+    got = torch.empty(M, N, device="cuda")
+    again = torch.empty(M, N, device="cuda")
+    assert _static(qa, qb, got, nc.capi.OUT_F32, M, N, K, 2) == nc.capi.OK
+    torch.cuda.synchronize()
+    free_before = torch.cuda.mem_get_info()[0]
+    reserved_before = torch.cuda.memory_reserved()
+    assert _static(qa, qb, got, nc.capi.OUT_F32, M, N, K, 4) == nc.capi.OK
+    assert _static(qa, qb, again, nc.capi.OUT_F32, M, N, K, 4) == nc.capi.OK
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info()[0] == free_before
+    assert torch.cuda.memory_reserved() == reserved_before
+    assert torch.equal(got, again)
