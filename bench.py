@@ -5,7 +5,8 @@
 A step is one rank's data-parallel GEMM workload of a d24 nanochat training step: every Linear of 24 layers
 (merged QKV, attention out, MLP fc, MLP proj) plus the lm_head in 2048-row chunks, each forward, dgrad and
 wgrad, with all MX quantizations of activations, gradients and (once per step) weights, weight gradients
-written as bf16 into one bucket and, for N > 1, reduce-scattered per layer over NCCL while backward continues
+written as bf16 into the reference's stacked send buffers and, for N > 1, reduce-scattered segment by segment
+(whole matrices per rank) over NCCL while backward continues
 (71.74 TFLOP of GEMM per rank and step). Inputs are seeded synthetic tensors of the BASELINE shapes and
 distributions; there is no dataset or checkpoint on this path.
 
@@ -34,6 +35,8 @@ METRIC = "MXFP8 linear TFLOP/s/GPU, d24 fwd+dgrad+wgrad shapes, % of FP8 tensor 
 WORKLOAD = "d24 data-parallel step GEMM set: 24 x (QKV, attn-out, MLP fc, MLP proj) + lm_head in 2048-row chunks, fwd+dgrad+wgrad, M=16384 tokens/rank"
 # 2MNK over the step's 305 GEMMs: 24 layers x 3 x 2 x 16384 x 12 x 1536^2 + lm_head 3 x 2 x 16384 x 32768 x 1536
 STEP_TFLOP = (24 * 3 * 2.0 * 16384 * 12 * 1536 ** 2 + 3 * 2.0 * 16384 * 32768 * 1536) / 1e12
+NCCL_MAX_CTAS = 0  # cap on the CTAs NCCL may use per collective (0: NCCL's default, which measured best: a cap of 8
+                   # or 4 slows the collective more than it frees SMs for the GEMMs it overlaps)
 FP8_SPEC_TFLOPS = 4500.0  # B200 dense FP8, 2x the 2.25e15 bf16 figure
 # dram__bytes_read.sum + dram__bytes_write.sum of one captured launch of the GEMM kernel, the merged-QKV forward
 # (M=16384, N=4608, K=1536, bf16 out), from the ncu summary of the pair kernel kept under profiles/. Its algorithmic
@@ -167,8 +170,16 @@ def run_gpu_arm(args):
         raise SystemExit("bench.py: no CUDA device; the MXFP8 engine has no CPU path")
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
+    nccl_max_ctas = int(os.environ.get("MXB200_NCCL_MAX_CTAS", str(NCCL_MAX_CTAS)))
     if world > 1:
-        dist.init_process_group("nccl", device_id=device)
+        # The collective overlaps GEMMs that want every SM (one CTA pair per TPC, all of shared memory): cap the CTAs
+        # NCCL's reduce-scatter kernel may take, so that it delays few tiles while it runs.
+        opts = dist.ProcessGroupNCCL.Options()
+        if nccl_max_ctas > 0:
+            opts.config.max_ctas = nccl_max_ctas
+        if os.environ.get("MXB200_NCCL_CGA"):
+            opts.config.cga_cluster_size = int(os.environ["MXB200_NCCL_CGA"])
+        dist.init_process_group("nccl", device_id=device, pg_options=opts)
 
     cfg = StepConfig()
     gemm_events, quant_events = [], []
@@ -352,7 +363,8 @@ def run_gpu_arm(args):
             "vs_baseline": None, "dtype": "fp8_e4m3 (ue8m0 block scales, fp32 accumulate)", "data": "synthetic",
             "config": {"workload": WORKLOAD, "tflop_per_rank_step": flops / 1e12, "global_tokens": cfg.tokens * world,
                        "parallelism": f"dp{world}", "l2": "operands and outputs of every launch exceed or rotate past the 126 MB L2 (9+ GB touched per step)",
-                       "collective": "bf16 reduce-scatter (avg) per layer over NCCL, overlapped" if world > 1 else "none (1 rank)"},
+                       "collective": (f"bf16 reduce-scatter (avg) of whole matrices per rank in the reference's stack segments over NCCL "
+                                      f"(max {nccl_max_ctas} CTAs), overlapped with backward") if world > 1 else "none (1 rank)"},
             "per_gpu_tflops": value / world,
             "pct_of_fp8_spec_peak": 100.0 * value / world / FP8_SPEC_TFLOPS,
             "pct_of_2x_measured_bf16_sustained": 100.0 * value / world / fp8_2x,

@@ -21,6 +21,7 @@
 // Every wait is bounded: after kWaitLimitNs a wait records its site in a device word, raises a CTA-wide abort
 // flag that all other waits poll, and the kernel drains and returns.
 #include <algorithm>
+#include <cmath>
 #include <mutex>
 
 #include <cuda.h>
@@ -361,7 +362,8 @@ __device__ __forceinline__ void store_rows_tma(const CUtensorMap* map_d, unsigne
   fence_proxy_async_smem();
   __syncwarp();
   if (lane == 0 && issue) {
-    tma_store_2d(map_d, stage, x, y);
+    // the output is not read again by this kernel: it should leave L2 before the operands do
+    tma_store_2d_hint(map_d, stage, x, y, l2_policy_evict_first());
     tma_store_commit();
   }
 }
@@ -1378,10 +1380,13 @@ TilePlan plan_tiles(int64_t M, int64_t N, int64_t K, int sms, bool need_pair = f
       for (int tn : {256, 192}) {
         const int64_t tiles = ((M + 255) / 256) * ((N + tn - 1) / tn);
         const int64_t units = tiles, iters = k_iters;
-        const int64_t waves = (units + t.slots - 1) / t.slots;
+        // Pairs draw their tiles from a counter, so with many short tiles per pair the launch ends within a fraction
+        // of a tile of the average share; with few long ones (the weight gradients) it ends on a whole round.
+        const double share = static_cast<double>(units) / t.slots;
+        const double waves = share >= 4.0 ? share + 0.25 : std::ceil(share);
         const double ingest = (16384.0 + tn * 64.0 + 1536.0) / 58.0;  // bytes a CTA loads per K step / (B/clk)
         const double per_tile = static_cast<double>(iters) * std::max(2.0 * tn, ingest) + (tn == 256 ? 1500.0 : 300.0);
-        const double cost = static_cast<double>(waves) * per_tile;
+        const double cost = waves * per_tile;
         if (best == 0.0 || cost < best * 0.995)
           best = cost, t.tile_n = tn;
       }

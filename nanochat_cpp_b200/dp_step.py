@@ -2,8 +2,8 @@
 
 Every Linear of a depth-`n_layer` nanochat model (merged QKV, attention out, MLP fc, MLP proj; then the
 chunked lm_head) runs forward, dgrad and wgrad through the MXFP8 engine on this rank's own micro-batch, the
-weight gradients leave as bf16 straight into one contiguous bucket, and each layer's slice of the bucket is
-reduce-scattered (average) across ranks while the next layer's backward runs. Nothing else of the model runs:
+weight gradients leave as bf16 straight into the reference's stacked send buffers, and every segment of whole
+matrices is reduce-scattered (average) across ranks as soon as backward has produced it, while backward goes on. Nothing else of the model runs:
 attention, norms and the loss are outside this path, so their outputs are seeded synthetic tensors of the
 right shape and distribution.
 
@@ -17,10 +17,26 @@ from __future__ import annotations
 from dataclasses import dataclass
 from typing import Callable, List, Optional
 
+import contextlib
+
 import torch
 import torch.distributed as dist
 
 from . import engine as nc
+
+
+@contextlib.contextmanager
+def nvtx_range(name: str):
+    """A named range on profiler timelines, as the reference's trainer marks its phases
+    (src/nanochat/train/trainer.cpp:284-312); a no-op without a profiler attached or a CUDA device."""
+    on = torch.cuda.is_available()
+    if on:
+        torch.cuda.nvtx.range_push(name)
+    try:
+        yield
+    finally:
+        if on:
+            torch.cuda.nvtx.range_pop()
 
 
 @dataclass
@@ -72,52 +88,123 @@ class StepConfig:
         return self.n_layer * layer + 3 * 2.0 * self.tokens * self.vocab * self.n_embd
 
 
+@dataclass
+class BucketSegment:
+    """One reduce-scatter: `count` matrices per rank out of world * count consecutive entries of a stack (or, for the
+    lm_head, one row slice per rank)."""
+    stack: str          # name of the stack, or "lm_head"
+    first: int          # first stack entry of the segment (world * entries-per-rank before it)
+    count: int          # entries each rank receives
+    out_first: int      # where they land in the rank's chunk of the stack
+    ready_layer: int    # backward has produced the segment once this layer's weight gradients are written
+
+
 class GradBucket:
-    """One contiguous bf16 buffer holding every weight gradient in backward order of use: segment i is layer i's
-    four matrices (qkv, attn_out, mlp_fc, mlp_proj), the last segment is lm_head. wgrad GEMMs write their bf16
-    output directly at these offsets, so no cast pass precedes the collective (the reference casts a stacked
-    fp32 buffer first, src/nanochat/train/optim.cpp:459). Each segment is reduce-scattered on its own: rank r
-    keeps elements [r * len / world, (r + 1) * len / world) of the segment, averaged over ranks."""
+    """The bf16 send buffers of the step's one collective, laid out as the reference's optimizer lays its gradients
+    out (src/nanochat/train/optim.cpp:699-714, 222-233, 437-472): the matrices of the transformer blocks are grouped
+    by shape, each group stacked as (K_pad, m, n) in forward order with K_pad a multiple of the world size,
+
+        muon_CxC   : per layer c_q, c_k, c_v, c_proj        (4 * n_layer entries; q, k, v adjacent, so the merged
+                                                             QKV weight gradient is one (3C, C) GEMM output)
+        muon_Cx4C  : per layer the MLP's c_proj             (n_layer entries)
+        muon_4CxC  : per layer the MLP's c_fc               (n_layer entries)
+
+    and every stack is reduce-scattered in at most eight segments: a segment is world * c consecutive entries, rank r
+    receives entries [r * c, (r + 1) * c) of it, so a rank always ends up with WHOLE matrices (Muon orthogonalises
+    per matrix). The lm_head gradient (an AdamW group) is scattered as row slices (optim.cpp:425-431). The weight
+    gradient GEMMs write their bf16 output straight into the stacks, so no cast pass precedes the collective (the
+    reference casts the stacked fp32 buffer first, optim.cpp:459)."""
+
+    MAX_SEGMENTS = 8  # kMuonSegments, optim.cpp:21
 
     def __init__(self, cfg: StepConfig, device, world: int = 1):
         self.cfg, self.world = cfg, world
-        self.segments: List[tuple] = []  # (offset, length)
+        C, L, V = cfg.n_embd, cfg.n_layer, cfg.vocab
+        if V % world:
+            raise ValueError("lm_head rows must divide evenly across ranks")
+        shapes = [("muon_CxC", 4 * L, C, C), ("muon_Cx4C", L, C, 4 * C), ("muon_4CxC", L, 4 * C, C)]
+        self.stack_info = {}
         off = 0
-        for _ in range(cfg.n_layer):
-            self.segments.append((off, cfg.layer_params))
-            off += cfg.layer_params
-        self.segments.append((off, cfg.lm_head_params))
-        off += cfg.lm_head_params
-        for _, length in self.segments:
-            if length % world:
-                raise ValueError("every bucket segment must divide evenly across ranks")
+        for name, count, m, n in shapes:
+            padded = (count + world - 1) // world * world
+            self.stack_info[name] = dict(count=count, padded=padded, m=m, n=n, offset=off)
+            off += padded * m * n
+        self.lm_offset = off
+        off += V * C
         self.numel = off
-        self.buffer = torch.empty(off, dtype=torch.bfloat16, device=device)
-        self.shards = [torch.empty(length // world, dtype=torch.bfloat16, device=device) for _, length in self.segments]
+        self.buffer = torch.zeros(off, dtype=torch.bfloat16, device=device)  # zeros: the padding entries stay zero
+        self.stacks = {name: self.buffer[i["offset"]:i["offset"] + i["padded"] * i["m"] * i["n"]].view(i["padded"], i["m"], i["n"])
+                       for name, i in self.stack_info.items()}
+        # this rank's chunks: (K_pad / world, m, n) per stack, (V / world, C) of the lm_head
+        self.chunks = {name: torch.empty((i["padded"] // world, i["m"], i["n"]), dtype=torch.bfloat16, device=device)
+                       for name, i in self.stack_info.items()}
+        self.lm_chunk = torch.empty((V // world, C), dtype=torch.bfloat16, device=device)
+        per_layer = {"muon_CxC": 4, "muon_Cx4C": 1, "muon_4CxC": 1}
+        self.segments: List[BucketSegment] = []
+        for name, i in self.stack_info.items():
+            chunk = i["padded"] // world
+            n_seg = min(self.MAX_SEGMENTS, chunk) if world > 1 else 1
+            counts = [chunk // n_seg + (1 if s < chunk % n_seg else 0) for s in range(n_seg)]
+            o = 0
+            for c in counts:
+                first = world * o
+                self.segments.append(BucketSegment(name, first, c, o, min(first // per_layer[name], L - 1)))
+                o += c
+        self.segments.append(BucketSegment("lm_head", 0, V // world, 0, L))
+        self.shards = [self.output(i).reshape(-1) for i in range(len(self.segments))]
 
+    # ---- where the GEMMs write
     def matrix(self, layer: int, index: int) -> torch.Tensor:
-        """The (out, in) gradient matrix `index` of `layer` as a view of the bucket."""
-        off = self.segments[layer][0]
-        for j, (_, n, k) in enumerate(self.cfg.linear_shapes):
-            if j == index:
-                return self.buffer[off:off + n * k].view(n, k)
-            off += n * k
+        """The (out, in) gradient of Linear `index` of `layer` (0 merged QKV, 1 attention out, 2 MLP fc, 3 MLP proj) as a
+        view of its stack."""
+        C = self.cfg.n_embd
+        if index == 0:
+            return self.stacks["muon_CxC"][4 * layer:4 * layer + 3].view(3 * C, C)
+        if index == 1:
+            return self.stacks["muon_CxC"][4 * layer + 3]
+        if index == 2:
+            return self.stacks["muon_4CxC"][layer]
+        if index == 3:
+            return self.stacks["muon_Cx4C"][layer]
         raise IndexError(index)
 
     def lm_head(self) -> torch.Tensor:
-        off, length = self.segments[-1]
-        return self.buffer[off:off + length].view(self.cfg.vocab, self.cfg.n_embd)
+        return self.buffer[self.lm_offset:].view(self.cfg.vocab, self.cfg.n_embd)
 
-    def segment(self, i: int) -> torch.Tensor:
-        off, length = self.segments[i]
-        return self.buffer[off:off + length]
+    # ---- the collective
+    def input(self, i: int) -> torch.Tensor:
+        """Segment i as sent: world * count whole matrices (or all rows of the lm_head)."""
+        seg = self.segments[i]
+        if seg.stack == "lm_head":
+            return self.lm_head()
+        return self.stacks[seg.stack][seg.first:seg.first + self.world * seg.count]
+
+    def output(self, i: int) -> torch.Tensor:
+        """Where this rank's share of segment i lands: entries [out_first, out_first + count) of its chunk."""
+        seg = self.segments[i]
+        if seg.stack == "lm_head":
+            return self.lm_chunk
+        return self.chunks[seg.stack][seg.out_first:seg.out_first + seg.count]
+
+    def owned_entries(self, stack: str, rank: int) -> List[int]:
+        """The stack entries rank `rank` holds after the scatter, in chunk order (optim.cpp:263-273)."""
+        rows = []
+        for seg in self.segments:
+            if seg.stack == stack:
+                rows += [seg.first + rank * seg.count + t for t in range(seg.count)]
+        return rows
+
+    def ready_after_layer(self, layer: int) -> List[int]:
+        """Segments that are complete once backward has finished `layer` (it walks the layers downwards; n_layer stands
+        for the lm_head, which comes first)."""
+        return [i for i, seg in enumerate(self.segments) if seg.ready_layer == layer]
 
     def reduce_scatter(self, i: int, group=None, async_op: bool = False):
-        """Average segment i across ranks into this rank's shard. world == 1: a copy."""
+        """Average segment i across ranks into this rank's chunk. world == 1: a copy."""
         if self.world == 1 or not dist.is_initialized():
-            self.shards[i].copy_(self.segment(i))
+            self.output(i).copy_(self.input(i)[:self.output(i).size(0)])
             return None
-        return dist.reduce_scatter_tensor(self.shards[i], self.segment(i), op=dist.ReduceOp.AVG, group=group,
+        return dist.reduce_scatter_tensor(self.output(i), self.input(i), op=dist.ReduceOp.AVG, group=group,
                                           async_op=async_op)
 
 
@@ -365,7 +452,9 @@ class DpStep:
         ev = torch.cuda.Event()
         ev.record()
         self.comm_stream.wait_event(ev)
-        with torch.cuda.stream(self.comm_stream):
+        seg = self.bucket.segments[i]
+        with nvtx_range(f"reduce_scatter {seg.stack}[{seg.first}:+{self.world * seg.count}]"), \
+                torch.cuda.stream(self.comm_stream):
             self._pending.append(self.bucket.reduce_scatter(i, async_op=True))
 
     def run_gemms_only(self, impl: str = "b200"):
@@ -390,14 +479,21 @@ class DpStep:
     def run_step(self, step: int = 0):
         cfg = self.cfg
         n_sets = len(self.x_attn)
-        self.quantize_weights()
+        with nvtx_range("quantize_weights"):
+            self.quantize_weights()
         for l in range(cfg.n_layer):
-            self.layer_forward(l, (step + l) % n_sets)
-        self.lm_head()
-        self._cast_grads(cfg.n_layer)
-        self._reduce_segment(cfg.n_layer)
+            with nvtx_range(f"layer{l}.forward"):
+                self.layer_forward(l, (step + l) % n_sets)
+        with nvtx_range("lm_head"):
+            self.lm_head()
+            self._cast_grads(cfg.n_layer)
+        for i in self.bucket.ready_after_layer(cfg.n_layer):
+            self._reduce_segment(i)
         for l in reversed(range(cfg.n_layer)):
-            self.layer_backward(l, (step + l) % n_sets)
-            self._cast_grads(l)
-            self._reduce_segment(l)
-        self.finish_collectives()
+            with nvtx_range(f"layer{l}.backward"):
+                self.layer_backward(l, (step + l) % n_sets)
+                self._cast_grads(l)
+            for i in self.bucket.ready_after_layer(l):
+                self._reduce_segment(i)
+        with nvtx_range("finish_collectives"):
+            self.finish_collectives()
