@@ -252,7 +252,7 @@ def run_gpu_arm(args):
     # (2) cuBLASLt MXFP8 at 8192^3 run for about two seconds: a measured FP8 GEMM rate of this GPU under its power cap;
     # (3) the step with the reference's default weight-gradient form (fp32 += into .grad, then the cast into the bucket)
     extra = {}
-    if world == 1:
+    if world == 1 and not args.no_comparators:
         def timed_ms(fn, reps):
             fn()
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -291,6 +291,9 @@ def run_gpu_arm(args):
             k[0] += 1
         extra["fp32_accumulate_ms"] = timed_ms(acc_step, min(args.steps, 5))
         step.set_wgrad_fp32_accumulate(False)
+        step.cfg.real_producers = True
+        extra["real_producers_ms"] = timed_ms(acc_step, min(args.steps, 5))
+        step.cfg.real_producers = False
         watchdog = watchdog or nc.capi.device_status()
 
     # ---- end to end: every step's micro-batch activations come from pinned host memory and a result slice goes back.
@@ -354,7 +357,7 @@ def run_gpu_arm(args):
         peak_source = (f"cuBLASLt MXFP8 8192^3 run for ~2 s in this process ({fp8_lt:.0f} TFLOP/s)" if fp8_lt and fp8_lt >= fp8_2x
                        else f"2 x bf16_tflops_sustained of {peaks['source']} ({fp8_2x:.0f} TFLOP/s)")
         cpu = None
-        if world == 1:
+        if world == 1 and not args.no_comparators:
             v, cores, sample = cpu_reference_sample()
             cpu = {"value": v, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample}
         line = {
@@ -372,13 +375,13 @@ def run_gpu_arm(args):
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             "gpu_launches": int(launches),
-            "roofline": {"bound": "tensor", "kernel": "mxb200_mx_gemm_pair_kernel (256x192 and 256x256 tiles)", "achieved": achieved, "peak": fp8_peak,
+            "roofline": {"bound": "tensor", "kernel": "mxb200_gemm_pair_256x256 / _256x192 (+ _relu_square, _relu_square_bwd)", "achieved": achieved, "peak": fp8_peak,
                          "unit": "TFLOP/s", "frac": achieved / fp8_peak, "traffic": GEMM_TRAFFIC_BYTES,
                          "traffic_launch": GEMM_TRAFFIC_LAUNCH,
                          "peak_source": peak_source, "peak_2x_bf16_sustained": fp8_2x, "peak_cublaslt_mxfp8_8192": fp8_lt,
                          "frac_of_fp8_spec_4500": achieved / FP8_SPEC_TFLOPS,
                          "launches": n_gemm, "avg_launch_us": gemm_ms * 1e3 / max(n_gemm, 1)},
-            "quantizer": {"bound": "hbm", "kernel": "mxb200_quantize_kernel", "achieved": cfg.quantized_bytes_per_step() * args.steps / (quant_ms * 1e-3) / 1e9,
+            "quantizer": {"bound": "hbm", "kernel": "mxb200_quantize_bf16 / mxb200_quantize_batch_f32", "achieved": cfg.quantized_bytes_per_step() * args.steps / (quant_ms * 1e-3) / 1e9,
                           "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": cfg.quantized_bytes_per_step() * args.steps / (quant_ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
                           "launches": n_quant, "ms_per_step": quant_ms / args.steps, "gb_per_step": cfg.quantized_bytes_per_step() / 1e9},
             "ms_per_step_split": {"gemm": gemm_ms / args.steps, "quantize": quant_ms / args.steps,
@@ -402,6 +405,13 @@ def run_gpu_arm(args):
                                              "value": flops / (extra["fp32_accumulate_ms"] * 1e-3) / 1e12, "unit": "TFLOP/s",
                                              "note": "the same step with every weight gradient as fp32 += into .grad and a cast into the bucket; "
                                                      "`value` above uses the single bf16 write into the bucket"}
+        if "real_producers_ms" in extra:
+            line["real_producers"] = {"ms_per_step": extra["real_producers_ms"],
+                                      "value": flops / (extra["real_producers_ms"] * 1e-3) / 1e12, "unit": "TFLOP/s",
+                                      "note": "the same step with the kernels a training step runs in front of the GEMMs: the fused residual "
+                                              "add + blend + RMS norm emitting MX for the QKV and MLP-fc inputs, and in the lm_head the softcap "
+                                              "loss pass + gradient quantized from the logits; `value` above uses BASELINE's ready-made tensors "
+                                              "and the plain quantizer"}
         if cpu is not None:
             line["cpu_baseline"] = cpu
         if watchdog != 0:
@@ -419,6 +429,8 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", type=str, default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-comparators", action="store_true",
+                    help="skip the cuBLASLt / fp32-accumulate / CPU legs (a short run of the step alone, for a profiler)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
     if args.impl == "reference":

@@ -369,9 +369,8 @@ __device__ __forceinline__ void store_rows_tma(const CUtensorMap* map_d, unsigne
 }
 
 template <int BN>
-__global__ void __launch_bounds__(kThreads, 1)
-      mxb200_mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                            const GemmParams p) {
+__device__ __forceinline__ void one_cta_kernel_body(const CUtensorMap* map_a, const CUtensorMap* map_b,
+                                                    const GemmParams& p) {
   using C = Config<BN>;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -399,8 +398,8 @@ __global__ void __launch_bounds__(kThreads, 1)
     fence_mbar_init();
   }
   if (warp == 0 && lane == 0) {
-    prefetch_tensormap(&map_a);
-    prefetch_tensormap(&map_b);
+    prefetch_tensormap(map_a);
+    prefetch_tensormap(map_b);
   }
   if (warp == 1) {
     tmem_alloc(&bars->tmem_base, kTmemCols);
@@ -434,8 +433,8 @@ __global__ void __launch_bounds__(kThreads, 1)
           }
           uint64_t* full = &bars->full[stage];
           mbar_arrive_expect_tx(el, full, tx);
-          tma_load_2d(el, s_a + stage * C::kABytes, &map_a, full, kt * kBK, tc.m * kBM);
-          tma_load_2d(el, s_b + stage * C::kBBytes, &map_b, full, kt * kBK, tc.n * BN);
+          tma_load_2d(el, s_a + stage * C::kABytes, map_a, full, kt * kBK, tc.m * kBM);
+          tma_load_2d(el, s_b + stage * C::kBBytes, map_b, full, kt * kBK, tc.n * BN);
           unsigned char* sf = s_sf + stage * C::kSfBytes;
           bulk_load(el, sf, sfa_src + static_cast<int64_t>(kt) * kScaleTileBytes, kScaleTileBytes, full);
           for (int j = 0; j < sfb_tiles; ++j)
@@ -866,7 +865,11 @@ template <int TN, int kFuse = kFuseNone>
 struct PairConfig {
   static_assert(TN == 192 || TN == 256, "tile width");
   static constexpr int kEpiBytes = kFuse == kFuseNone ? kEpiStageBytes : kEpiFusedBytes;
+#ifdef MXB200_EXP_PARTS2
+  static constexpr int kParts = 2;
+#else
   static constexpr int kParts = kFuse == kFuseNone ? 2 : 3;
+#endif
   static constexpr int kEpiWarps = 4 * kParts;
   static constexpr int kEpiThreads = 32 * kEpiWarps;
   static constexpr int kThreads = 64 + kEpiThreads;
@@ -877,7 +880,11 @@ struct PairConfig {
   static constexpr uint32_t kBBytes = kBRows * kBK;
   static constexpr uint32_t kSfBytes = kScaleTileBytes * (1 + kSfbTiles);  // A: own 128 rows; B: all its tiles
   static constexpr uint32_t kTxPerCta = kABytes + kBBytes + kSfBytes;
+#ifdef MXB200_EXP_PARTS2
+  static constexpr int kStages = (TN == 192 ? 7 : 6) - (kFuse == kFuseNone ? 0 : 1);
+#else
   static constexpr int kStages = (TN == 192 ? 7 : 6) - (kFuse == kFuseNone ? 0 : 2);
+#endif
   static constexpr bool kOverlap = TN == 256;
   static constexpr uint32_t kAcc0 = 0, kAcc1 = kOverlap ? 224 : TN;
   static constexpr uint32_t kSfaCol = kOverlap ? 480 : 2 * TN, kSfbCol = kSfaCol + 4;
@@ -887,15 +894,14 @@ struct PairConfig {
   static_assert(sizeof(Barriers) <= 512, "barrier block");
 };
 
+// The kernel body; the kernels themselves are the non-template functions at the end of this file (plain global
+// names read the same in every profiler). The tensor maps stay in the kernels' parameter space and come by address.
 template <int TN, int kFuse>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairConfig<TN, kFuse>::kThreads, 1)
-      mxb200_mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                                 const __grid_constant__ CUtensorMap map_sfa,
-                                 const __grid_constant__ CUtensorMap map_sfb,
-                                 const __grid_constant__ CUtensorMap map_d,
-                                 const __grid_constant__ CUtensorMap map_part,
-                                 const __grid_constant__ CUtensorMap map_q,
-                                 const __grid_constant__ CUtensorMap map_qt, const GemmParams p) {
+__device__ __forceinline__ void pair_kernel_body(const CUtensorMap* map_a, const CUtensorMap* map_b,
+                                                 const CUtensorMap* map_sfa, const CUtensorMap* map_sfb,
+                                                 const CUtensorMap* map_d, const CUtensorMap* map_part,
+                                                 const CUtensorMap* map_q, const CUtensorMap* map_qt,
+                                                 const GemmParams& p) {
   using C = PairConfig<TN, kFuse>;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -932,16 +938,16 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairConfig<TN, kFuse
     fence_mbar_init();
   }
   if (warp == 0 && lane == 0) {
-    prefetch_tensormap(&map_a);
-    prefetch_tensormap(&map_b);
-    prefetch_tensormap(&map_sfa);
-    prefetch_tensormap(&map_sfb);
-    prefetch_tensormap(&map_d);
+    prefetch_tensormap(map_a);
+    prefetch_tensormap(map_b);
+    prefetch_tensormap(map_sfa);
+    prefetch_tensormap(map_sfb);
+    prefetch_tensormap(map_d);
     if (p.splits > 1)
-      prefetch_tensormap(&map_part);
+      prefetch_tensormap(map_part);
     if (kFuse != kFuseNone) {
-      prefetch_tensormap(&map_q);
-      prefetch_tensormap(&map_qt);
+      prefetch_tensormap(map_q);
+      prefetch_tensormap(map_qt);
     }
   }
   if (warp == 1) {
@@ -1015,10 +1021,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairConfig<TN, kFuse
           mbar_arrive_expect_tx(el_leader, full0 + stage * 8, 2 * C::kTxPerCta);
           const uint32_t full = full_leader0 + stage * 8;
           const uint32_t sf = sf0 + stage * C::kSfBytes;
-          tma_load_2d_pair(el, a0 + stage * C::kABytes, &map_a, full, kt * kBK, row_a);
-          tma_load_2d_pair(el, b0 + stage * C::kBBytes, &map_b, full, kt * kBK, row_b);
-          tma_load_4d_pair(el, sf, &map_sfa, full, 0, 0, kt, sfa_tile);
-          tma_load_4d_pair(el, sf + kScaleTileBytes, &map_sfb, full, 0, 0, kt, sfb_tile);
+          tma_load_2d_pair(el, a0 + stage * C::kABytes, map_a, full, kt * kBK, row_a);
+          tma_load_2d_pair(el, b0 + stage * C::kBBytes, map_b, full, kt * kBK, row_b);
+          tma_load_4d_pair(el, sf, map_sfa, full, 0, 0, kt, sfa_tile);
+          tma_load_4d_pair(el, sf + kScaleTileBytes, map_sfb, full, 0, 0, kt, sfb_tile);
           if (++stage == C::kStages) {
             stage = 0;
             phase ^= 1u;
@@ -1188,10 +1194,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairConfig<TN, kFuse
         if (part != nullptr) {
           // split-K partials take the same TMA store path: the workspace is a (half tiles x 128 rows, TN) matrix
           const int part_row0 = static_cast<int>(half_index) * 128 + quarter * 32;
-          store_rows_tma(&map_part, stage, lane, r[i & 1], c * 32, part_row0, true);
-          store_rows_tma(&map_part, stage, lane, r[i & 1] + 16, c * 32 + 16, part_row0, true);
+          store_rows_tma(map_part, stage, lane, r[i & 1], c * 32, part_row0, true);
+          store_rows_tma(map_part, stage, lane, r[i & 1] + 16, c * 32 + 16, part_row0, true);
         } else if constexpr (kFuse != kFuseNone) {
-          fused_quantize_chunk<kFuse>(p, &map_d, &map_q, &map_qt, stage, lane, reinterpret_cast<const float*>(r[i & 1]),
+          fused_quantize_chunk<kFuse>(p, map_d, map_q, map_qt, stage, lane, reinterpret_cast<const float*>(r[i & 1]),
                                       row, col, warp_row0, row_ok && col < p.N, h_pieces,
                                       i + 1 < n_mine ? col0 + chunk_of(i + 1) * 32 : -1);
         } else {
@@ -1199,9 +1205,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairConfig<TN, kFuse
           const bool issue = warp_row0 < p.M && col < p.N;
           uint32_t o[32];
           compute_chunk(p, alpha, row, col, reinterpret_cast<const float*>(r[i & 1]), valid, o);
-          store_rows_tma(&map_d, stage, lane, o, col, warp_row0, issue);
+          store_rows_tma(map_d, stage, lane, o, col, warp_row0, issue);
           if (p.out_kind == kOutF32)
-            store_rows_tma(&map_d, stage, lane, o + 16, col + 16, warp_row0, issue);
+            store_rows_tma(map_d, stage, lane, o + 16, col + 16, warp_row0, issue);
         }
       }
       tcgen05_fence_before_sync();
@@ -1290,6 +1296,63 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairConfig<TN, kFuse
     tcgen05_fence_after_sync();
     tmem_dealloc_pair(tmem_base, kTmemCols);
   }
+}
+
+}  // namespace
+}  // namespace mxb200
+
+// ------------------------------------------------------------------------------------------------ kernels
+//
+// Global, non-template kernels with plain mxb200_* names, as nanochat-cpp names its own
+// (src/nanochat/model/fp8/fp8_kernel.cu:174-175): a launch list or a timeline shows which tile shape and which
+// epilogue ran without decoding template arguments. <rows>x<columns> is the output tile; the CTA-pair kernels share
+// it between the two SMs of a TPC.
+#define MXB200_GEMM_KERNEL(name, BN)                                                                                   \
+  __global__ void __launch_bounds__(mxb200::kThreads, 1) name(const __grid_constant__ CUtensorMap map_a,               \
+                                                              const __grid_constant__ CUtensorMap map_b,               \
+                                                              const mxb200::GemmParams p) {                            \
+    mxb200::one_cta_kernel_body<BN>(&map_a, &map_b, p);                                                                \
+  }
+
+#define MXB200_GEMM_PAIR_KERNEL(name, TN, FUSE)                                                                        \
+  __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(mxb200::PairConfig<TN, FUSE>::kThreads, 1)               \
+        name(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,                     \
+             const __grid_constant__ CUtensorMap map_sfa, const __grid_constant__ CUtensorMap map_sfb,                 \
+             const __grid_constant__ CUtensorMap map_d, const __grid_constant__ CUtensorMap map_part,                  \
+             const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_qt,                    \
+             const mxb200::GemmParams p) {                                                                             \
+    mxb200::pair_kernel_body<TN, FUSE>(&map_a, &map_b, &map_sfa, &map_sfb, &map_d, &map_part, &map_q, &map_qt, p);     \
+  }
+
+MXB200_GEMM_KERNEL(mxb200_gemm_128x128, 128)
+MXB200_GEMM_KERNEL(mxb200_gemm_128x256, 256)
+MXB200_GEMM_PAIR_KERNEL(mxb200_gemm_pair_256x192, 192, mxb200::kFuseNone)
+MXB200_GEMM_PAIR_KERNEL(mxb200_gemm_pair_256x256, 256, mxb200::kFuseNone)
+MXB200_GEMM_PAIR_KERNEL(mxb200_gemm_pair_256x192_relu_square, 192, mxb200::kFuseReluSquare)
+MXB200_GEMM_PAIR_KERNEL(mxb200_gemm_pair_256x256_relu_square, 256, mxb200::kFuseReluSquare)
+MXB200_GEMM_PAIR_KERNEL(mxb200_gemm_pair_256x192_relu_square_bwd, 192, mxb200::kFuseReluSquareBwd)
+MXB200_GEMM_PAIR_KERNEL(mxb200_gemm_pair_256x256_relu_square_bwd, 256, mxb200::kFuseReluSquareBwd)
+
+namespace mxb200 {
+namespace {
+
+using GemmKernel = void (*)(CUtensorMap, CUtensorMap, GemmParams);
+using GemmPairKernel = void (*)(CUtensorMap, CUtensorMap, CUtensorMap, CUtensorMap, CUtensorMap, CUtensorMap, CUtensorMap,
+                                CUtensorMap, GemmParams);
+
+template <int BN>
+constexpr GemmKernel one_cta_kernel() {
+  return BN == 256 ? mxb200_gemm_128x256 : mxb200_gemm_128x128;
+}
+
+template <int TN, int kFuse>
+constexpr GemmPairKernel pair_kernel() {
+  if constexpr (kFuse == kFuseReluSquare)
+    return TN == 256 ? mxb200_gemm_pair_256x256_relu_square : mxb200_gemm_pair_256x192_relu_square;
+  else if constexpr (kFuse == kFuseReluSquareBwd)
+    return TN == 256 ? mxb200_gemm_pair_256x256_relu_square_bwd : mxb200_gemm_pair_256x192_relu_square_bwd;
+  else
+    return TN == 256 ? mxb200_gemm_pair_256x256 : mxb200_gemm_pair_256x192;
 }
 
 // ------------------------------------------------------------------------------------------------ host side
@@ -1425,9 +1488,9 @@ int set_smem_once(Kernel kernel, size_t bytes, bool* configured) {
 template <int BN>
 int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, int grid, cudaStream_t stream) {
   static bool configured[64] = {};
-  if (int st = set_smem_once(mxb200_mx_gemm_kernel<BN>, Config<BN>::kSmemBytes, configured); st != MXB200_OK)
+  if (int st = set_smem_once(one_cta_kernel<BN>(), Config<BN>::kSmemBytes, configured); st != MXB200_OK)
     return st;
-  mxb200_mx_gemm_kernel<BN><<<grid, kThreads, Config<BN>::kSmemBytes, stream>>>(ma, mb, p);
+  one_cta_kernel<BN>()<<<grid, kThreads, Config<BN>::kSmemBytes, stream>>>(ma, mb, p);
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return launch_status();
 }
@@ -1440,9 +1503,9 @@ template <int TN, int kFuse>
 int launch_pair(const PairMaps& m, const GemmParams& p, int pairs, cudaStream_t stream) {
   using C = PairConfig<TN, kFuse>;
   static bool configured[64] = {};
-  if (int st = set_smem_once(mxb200_mx_gemm_pair_kernel<TN, kFuse>, C::kSmemBytes, configured); st != MXB200_OK)
+  if (int st = set_smem_once(pair_kernel<TN, kFuse>(), C::kSmemBytes, configured); st != MXB200_OK)
     return st;
-  mxb200_mx_gemm_pair_kernel<TN, kFuse><<<2 * pairs, C::kThreads, C::kSmemBytes, stream>>>(m.a, m.b, m.sfa, m.sfb, m.d,
+  pair_kernel<TN, kFuse>()<<<2 * pairs, C::kThreads, C::kSmemBytes, stream>>>(m.a, m.b, m.sfa, m.sfb, m.d,
                                                                                           m.part, m.q, m.qt, p);
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return launch_status();

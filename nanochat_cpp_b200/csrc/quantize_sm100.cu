@@ -337,12 +337,6 @@ __device__ __forceinline__ void quantize_tile(const QuantParams& p, int tile_ind
   }
 }
 
-template <bool kIn32, int kPro>
-__global__ void __launch_bounds__(kThreads, (kIn32 || kPro == kSoftcapGrad) ? 2 : (kPro == kReluSquareBwd ? 3 : 4))
-      mxb200_quantize_kernel(const QuantParams p) {
-  quantize_tile<kIn32, kPro>(p, static_cast<int>(blockIdx.x));
-}
-
 // Several tensors in one launch: a weight matrix of a d12-d26 model is 36 to 700 tiles, under one or two waves of
 // the machine, so a launch per weight is bound by its own ramp-up and tail (12 us for 14 MB). The tiles of up to
 // kMaxBatch tensors are numbered through; a CTA finds its tensor by its first tile.
@@ -363,8 +357,9 @@ struct BatchParams {
   bool floor_rule;
 };
 
+// One CTA of the batched launch: finds its tensor by its first tile.
 template <bool kIn32>
-__global__ void __launch_bounds__(kThreads, kIn32 ? 2 : 4) mxb200_quantize_batch_kernel(const __grid_constant__ BatchParams bp) {
+__device__ __forceinline__ void quantize_batch_tile(const BatchParams& bp) {
   int j = 0;
   const int tile = static_cast<int>(blockIdx.x);
   while (j + 1 < bp.n && tile >= bp.jobs[j + 1].first_tile)
@@ -373,6 +368,54 @@ __global__ void __launch_bounds__(kThreads, kIn32 ? 2 : 4) mxb200_quantize_batch
   QuantParams p{job.x,      nullptr,         job.ld, job.out, job.out_t, job.tiles_c, bp.floor_rule,
                 job.wide_in, job.wide_out_t, SoftcapGrad{}};
   quantize_tile<kIn32, kNone>(p, tile - job.first_tile);
+}
+
+}  // namespace
+}  // namespace mxb200
+
+// Kernels: global, non-template, plain mxb200_* names, as nanochat-cpp names its own
+// (src/nanochat/model/fp8/fp8_kernel.cu:174-175, 197-210). CTAs per SM: four for bf16 input, fewer where a prologue or
+// fp32 input needs more registers or shared memory per CTA.
+#define MXB200_QUANTIZE_KERNEL(name, IN32, PRO, CTAS)                                                                  \
+  __global__ void __launch_bounds__(mxb200::kThreads, CTAS) name(const mxb200::QuantParams p) {                        \
+    mxb200::quantize_tile<IN32, PRO>(p, static_cast<int>(blockIdx.x));                                                 \
+  }
+#define MXB200_QUANTIZE_BATCH_KERNEL(name, IN32, CTAS)                                                                 \
+  __global__ void __launch_bounds__(mxb200::kThreads, CTAS) name(const __grid_constant__ mxb200::BatchParams bp) {     \
+    mxb200::quantize_batch_tile<IN32>(bp);                                                                             \
+  }
+
+MXB200_QUANTIZE_KERNEL(mxb200_quantize_bf16, false, mxb200::kNone, 4)
+MXB200_QUANTIZE_KERNEL(mxb200_quantize_f32, true, mxb200::kNone, 2)
+MXB200_QUANTIZE_KERNEL(mxb200_quantize_relu_square, false, mxb200::kReluSquare, 4)
+MXB200_QUANTIZE_KERNEL(mxb200_quantize_relu_square_bwd, false, mxb200::kReluSquareBwd, 3)
+MXB200_QUANTIZE_KERNEL(mxb200_quantize_softcap_grad, false, mxb200::kSoftcapGrad, 2)
+MXB200_QUANTIZE_BATCH_KERNEL(mxb200_quantize_batch_bf16, false, 4)
+MXB200_QUANTIZE_BATCH_KERNEL(mxb200_quantize_batch_f32, true, 2)
+
+namespace mxb200 {
+namespace {
+
+using QuantKernel = void (*)(QuantParams);
+using QuantBatchKernel = void (*)(BatchParams);
+
+template <bool kIn32, int kPro>
+constexpr QuantKernel quantize_kernel() {
+  if constexpr (kIn32)
+    return mxb200_quantize_f32;
+  else if constexpr (kPro == kReluSquare)
+    return mxb200_quantize_relu_square;
+  else if constexpr (kPro == kReluSquareBwd)
+    return mxb200_quantize_relu_square_bwd;
+  else if constexpr (kPro == kSoftcapGrad)
+    return mxb200_quantize_softcap_grad;
+  else
+    return mxb200_quantize_bf16;
+}
+
+template <bool kIn32>
+constexpr QuantBatchKernel quantize_batch_kernel() {
+  return kIn32 ? mxb200_quantize_batch_f32 : mxb200_quantize_batch_bf16;
 }
 
 int check_out(const mxb200_mx_out& o, int64_t ld_min) {
@@ -394,12 +437,12 @@ int launch(const QuantParams& p, int64_t tiles, cudaStream_t stream) {
   int device = 0;
   cudaGetDevice(&device);
   if (smem > 48 * 1024 && configured_for.load() != device) {
-    if (cudaFuncSetAttribute(mxb200_quantize_kernel<kIn32, kPro>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (cudaFuncSetAttribute(quantize_kernel<kIn32, kPro>(), cudaFuncAttributeMaxDynamicSharedMemorySize,
                              static_cast<int>(smem)) != cudaSuccess)
       return MXB200_ERR_LAUNCH;
     configured_for.store(device);
   }
-  mxb200_quantize_kernel<kIn32, kPro><<<static_cast<unsigned>(tiles), kThreads, smem, stream>>>(p);
+  quantize_kernel<kIn32, kPro>()<<<static_cast<unsigned>(tiles), kThreads, smem, stream>>>(p);
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return launch_status();
 }
@@ -460,12 +503,12 @@ int launch_batch(const BatchParams& bp, int tiles, cudaStream_t stream) {
   int device = 0;
   cudaGetDevice(&device);
   if (smem > 48 * 1024 && configured_for.load() != device) {
-    if (cudaFuncSetAttribute(mxb200_quantize_batch_kernel<kIn32>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (cudaFuncSetAttribute(quantize_batch_kernel<kIn32>(), cudaFuncAttributeMaxDynamicSharedMemorySize,
                              static_cast<int>(smem)) != cudaSuccess)
       return MXB200_ERR_LAUNCH;
     configured_for.store(device);
   }
-  mxb200_quantize_batch_kernel<kIn32><<<static_cast<unsigned>(tiles), kThreads, smem, stream>>>(bp);
+  quantize_batch_kernel<kIn32>()<<<static_cast<unsigned>(tiles), kThreads, smem, stream>>>(bp);
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return launch_status();
 }

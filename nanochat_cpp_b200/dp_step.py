@@ -54,6 +54,12 @@ class StepConfig:
     # (src/nanochat/model/fp8/fp8.cpp:470-514) followed by the cast of each layer's gradients into the bucket
     # (src/nanochat/train/optim.cpp:459).
     wgrad_fp32_accumulate: bool = False
+    # Producers of the quantized GEMM inputs: False = the plain quantizer on ready-made bf16 tensors everywhere (the
+    # BASELINE configurations' form: they time Linears, not what feeds them); True = the kernels the reference's
+    # training step actually runs there: the fused residual add + lambda blend + RMS norm that emits MX for the QKV
+    # and MLP-fc inputs (src/nanochat/model/ops/residual_norm.cpp:33-96) and, in the lm_head, the softcap loss pass
+    # and the gradient quantized straight from the logits (ops/softcap_ce.cpp:66-92) instead of synthetic dlogits.
+    real_producers: bool = False
 
     @property
     def linear_shapes(self):
@@ -280,6 +286,8 @@ class DpStep:
         # fp32 .grad buffers, only for the accumulate form
         self.grads = self.grad_lm = None
         self.set_wgrad_fp32_accumulate(cfg.wgrad_fp32_accumulate)
+        # inputs of the real producers (StepConfig.real_producers), allocated on first use
+        self._producer_state = None
         # "b200": this library; "cublaslt": the same GEMMs through torch._scaled_mm, the arithmetic of the
         # reference's --gemm=cublas (src/nanochat/model/fp8/mx_gemm.cpp:158); gemm_only: replay the GEMMs over the
         # operands quantized by an earlier step, no quantizer launches
@@ -297,6 +305,44 @@ class DpStep:
             self.grads = [[torch.zeros((n, k), dtype=torch.float32, device=device) for _, n, k in cfg.linear_shapes]
                           for _ in range(cfg.n_layer)]
             self.grad_lm = torch.zeros((cfg.vocab, cfg.n_embd), dtype=torch.float32, device=device)
+
+    def _producers(self):
+        """Buffers of the real-producer form: a residual stream x0 and lambdas for the blend, outputs of the two fused
+        residual steps per layer, targets and per-row loss buffers of the lm_head."""
+        if self._producer_state is None:
+            cfg, dev = self.cfg, self.device
+            M, C = cfg.tokens, cfg.n_embd
+            g = torch.Generator(device=dev).manual_seed(77 + self.rank)
+            bf = torch.bfloat16
+            st = {}
+            st["x0"] = torch.randn((M, C), generator=g, device=dev).to(bf)
+            st["lr"] = torch.rand(cfg.n_layer, generator=g, device=dev) + 0.5
+            st["l0"] = torch.rand(cfg.n_layer, generator=g, device=dev) * 0.3
+            st["targets"] = torch.randint(0, cfg.vocab, (M,), generator=g, device=dev)
+            st["loss"] = torch.empty(M, dtype=torch.float32, device=dev)
+            st["lse"] = torch.empty(cfg.chunk_rows, dtype=torch.float32, device=dev)
+            st["scale"] = torch.full((1,), 1.0 / M, device=dev)
+            # (res, n, n_mx, rstd, s) per fused residual step; n_mx is replaced by the layer's saved MX buffers
+            st["attn_out"] = [None] * cfg.n_layer
+            st["mlp_out"] = [None] * cfg.n_layer
+            self._producer_state = st
+        return self._producer_state
+
+    def _residual_norm(self, key: str, l: int, x, r, x0, q: nc.Fp8Tensor):
+        """One fused residual step whose MX output lands in the saved-for-backward buffers q."""
+        st = self._producers()
+        if self.gemm_only:
+            return
+        if self.qhook:
+            self.qhook(True)
+        prev = st[key][l]
+        if prev is None:
+            res, n, n_mx, rstd, s_ = nc.residual_norm_mx(x, r, x0, st["lr"], st["l0"], l)
+            prev = (res, n, q, rstd, s_)  # from now on the kernel writes MX straight into q
+            del n_mx
+        st[key][l] = nc.residual_norm_mx(x, r, x0, st["lr"], st["l0"], l, out=prev)
+        if self.qhook:
+            self.qhook(False)
 
     def _grad(self, layer: int, index: int):
         return self.grads[layer][index] if self.cfg.wgrad_fp32_accumulate else None
@@ -370,11 +416,17 @@ class DpStep:
 
     def layer_forward(self, l: int, s: int):
         wq = self.wq[l]
-        self._quant(self.x_attn[s], self.xq_attn[l])
+        if self.cfg.real_producers:  # s = x + r, res = lr s + l0 x0, n = rms_norm(res) -> MX (the QKV input)
+            self._residual_norm("attn_out", l, self.x_attn[s], self.resid[s], self._producers()["x0"], self.xq_attn[l])
+        else:
+            self._quant(self.x_attn[s], self.xq_attn[l])
         self._gemm(self.qkv, self.xq_attn[l].data, self.xq_attn[l].inv_scale, wq[0].data, wq[0].inv_scale)
         self._quant(self.y_att[s], self.yq_att[l])
         self._gemm(self.out_c, self.yq_att[l].data, self.yq_att[l].inv_scale, wq[1].data, wq[1].inv_scale, self.resid[s])
-        self._quant(self.x_mlp[s], self.xq_mlp[l])
+        if self.cfg.real_producers:  # res = x + r, n = rms_norm(res) -> MX (the MLP fc input)
+            self._residual_norm("mlp_out", l, self.x_mlp[s], self.resid[s], None, self.xq_mlp[l])
+        else:
+            self._quant(self.x_mlp[s], self.xq_mlp[l])
         if self.cfg.fused_mlp and not self.gemm_only:
             # fc GEMM writes h and, from the same epilogue, MX(relu(h)^2) in both layouts (fp8.cpp:279-284)
             if self.hook:
@@ -436,9 +488,20 @@ class DpStep:
             xa = self.xq_lm.data[begin:begin + rows]
             xs = self.xq_lm.inv_scale[begin * K // 32:(begin + rows) * K // 32]
             self._gemm(self.logits, xa, xs, self.wq_lm.data, self.wq_lm.inv_scale)
-            g = self.dlogits[c % len(self.dlogits)]
-            self._quant_into(g, False, nc.mx_out(self.gq_lm.data, self.gq_lm.inv_scale, begin, 0),
-                             nc.mx_out(self.gq_lm.data_t, self.gq_lm.inv_scale_t, 0, begin))
+            out_rows = nc.mx_out(self.gq_lm.data, self.gq_lm.inv_scale, begin, 0)
+            out_cols = nc.mx_out(self.gq_lm.data_t, self.gq_lm.inv_scale_t, 0, begin)
+            if self.cfg.real_producers and not self.gemm_only:
+                st = self._producers()
+                if self.qhook:
+                    self.qhook(True)
+                t = st["targets"][begin:begin + rows]
+                nc.softcap_ce_loss(self.logits, t, cfg.vocab, 15.0, loss=st["loss"][begin:begin + rows], lse=st["lse"])
+                nc.softcap_ce_grad_mx(self.logits, t, st["lse"], cfg.vocab, 15.0, out_rows, out_cols, grad_scale=st["scale"])
+                if self.qhook:
+                    self.qhook(False)
+            else:
+                g = self.dlogits[c % len(self.dlogits)]
+                self._quant_into(g, False, out_rows, out_cols)
             ga = self.gq_lm.data[begin:begin + rows]
             gs = self.gq_lm.inv_scale[begin * cfg.vocab // 32:(begin + rows) * cfg.vocab // 32]
             self._gemm(self.dx_lm[begin:begin + rows], ga, gs, self.wq_lm.data_t, self.wq_lm.inv_scale_t)
