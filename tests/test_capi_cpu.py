@@ -74,8 +74,12 @@ def test_bucket_layout():
     b = GradBucket(cfg, torch.device("cpu"), world=1)
     assert b.numel == 2 * cfg.layer_params + cfg.lm_head_params
     assert cfg.layer_params == 12 * 256 * 256
+    # the reference's stacks by shape: (C, C) x 4 per layer, then (C, 4C), then (4C, C); layer 1's MLP fc gradient is
+    # entry 1 of the last one
     m = b.matrix(1, 2)
     assert m.shape == (1024, 256)
-    assert m.data_ptr() == b.buffer.data_ptr() + 2 * (cfg.layer_params + 3 * 256 * 256 + 256 * 256)
+    cc, c4c = 8 * 256 * 256, 2 * 256 * 1024
+    assert m.data_ptr() == b.buffer.data_ptr() + 2 * (cc + c4c + 1024 * 256)
+    assert b.matrix(1, 0).data_ptr() == b.buffer.data_ptr() + 2 * (4 * 256 * 256)
     assert b.lm_head().shape == (512, 256)
     assert abs(StepConfig().flops_per_step() / 1e12 - 71.743) < 0.01
