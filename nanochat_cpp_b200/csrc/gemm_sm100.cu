@@ -135,6 +135,7 @@ struct Barriers {
   uint32_t tmem_base;
   uint32_t abort_flag;
   uint32_t last_flag;
+  uint32_t scale_done[2];  // fused quantizer, 256-wide tile: epilogue warps done with the tile in accumulator buffer 0 / 1
   // CTA-pair kernel, tile scheduler: the leader CTA's producer draws unit indices from a global counter and posts each
   // to both CTAs (sched_unit, sched_full); every other role of the pair reads it and reports to the leader's sched_empty
   uint64_t sched_full[4];
@@ -688,7 +689,8 @@ template <int kFuse>
 __device__ __forceinline__ void fused_quantize_chunk(const GemmParams& p, const CUtensorMap* map_d,
                                                      const CUtensorMap* map_q, const CUtensorMap* map_qt,
                                                      unsigned char* stage, int lane, const float* acc, int64_t row,
-                                                     int col, int warp_row0, bool valid, uint4* h_pieces, int next_col) {
+                                                     int col, int warp_row0, bool valid, uint4* h_pieces, int next_col,
+                                                     unsigned char* scale_stage, int chunk) {
   unsigned char* st_out = stage;         // TMA source (forward form); h hand-over buffer (backward form, never a source)
   unsigned char* st_tr = stage + 2048;   // transpose tile, only ever touched by this warp's threads
   unsigned char* st_q = stage + 4096;    // TMA source
@@ -771,17 +773,26 @@ __device__ __forceinline__ void fused_quantize_chunk(const GemmParams& p, const 
     e_col = quantize_block(c, p.floor_rule, wqt);
   }
 
-  // ---- results out: scale bytes straight to their swizzled positions, data through the staging tiles
-  if (valid) {
-    const int b = col >> 5;
-    p.q_scale[(static_cast<int64_t>(row >> 7) * p.q_scale_tiles + (b >> 2)) * kScaleTileBytes +
-              mx_scale_tile_offset(static_cast<int>(row & 127), b)] = static_cast<uint8_t>(e_row);
-  }
+  // ---- results out: data through the staging tiles; scale bytes into the CTA's shared-memory copy of its four scale
+  // tiles (written out whole once the half tile is done: a byte store to global memory costs a 32-byte sector of
+  // the SM's path to L2, a third more write traffic for the kernel), or, without one, straight to their swizzled
+  // positions
   const int n = col + lane;  // row of the transposed layout
-  if (warp_row0 < p.M && n < p.N) {
-    const int b = warp_row0 >> 5;
-    p.qt_scale[(static_cast<int64_t>(n >> 7) * p.qt_scale_tiles + (b >> 2)) * kScaleTileBytes +
-               mx_scale_tile_offset(n & 127, b)] = static_cast<uint8_t>(e_col);
+  if (scale_stage != nullptr) {
+    const int t = chunk >> 2;  // which of the tile's two 128-column groups
+    scale_stage[t * kScaleTileBytes + mx_scale_tile_offset(static_cast<int>(row & 127), chunk)] = static_cast<uint8_t>(e_row);
+    scale_stage[(2 + t) * kScaleTileBytes + mx_scale_tile_offset(n & 127, warp_row0 >> 5)] = static_cast<uint8_t>(e_col);
+  } else {
+    if (valid) {
+      const int b = col >> 5;
+      p.q_scale[(static_cast<int64_t>(row >> 7) * p.q_scale_tiles + (b >> 2)) * kScaleTileBytes +
+                mx_scale_tile_offset(static_cast<int>(row & 127), b)] = static_cast<uint8_t>(e_row);
+    }
+    if (warp_row0 < p.M && n < p.N) {
+      const int b = warp_row0 >> 5;
+      p.qt_scale[(static_cast<int64_t>(n >> 7) * p.qt_scale_tiles + (b >> 2)) * kScaleTileBytes +
+                 mx_scale_tile_offset(n & 127, b)] = static_cast<uint8_t>(e_col);
+    }
   }
   if (lane == 0)
     tma_store_wait_read<0>();  // the previous chunk's stores have been read out of the staging tiles
@@ -865,11 +876,7 @@ template <int TN, int kFuse = kFuseNone>
 struct PairConfig {
   static_assert(TN == 192 || TN == 256, "tile width");
   static constexpr int kEpiBytes = kFuse == kFuseNone ? kEpiStageBytes : kEpiFusedBytes;
-#ifdef MXB200_EXP_PARTS2
-  static constexpr int kParts = 2;
-#else
   static constexpr int kParts = kFuse == kFuseNone ? 2 : 3;
-#endif
   static constexpr int kEpiWarps = 4 * kParts;
   static constexpr int kEpiThreads = 32 * kEpiWarps;
   static constexpr int kThreads = 64 + kEpiThreads;
@@ -880,16 +887,16 @@ struct PairConfig {
   static constexpr uint32_t kBBytes = kBRows * kBK;
   static constexpr uint32_t kSfBytes = kScaleTileBytes * (1 + kSfbTiles);  // A: own 128 rows; B: all its tiles
   static constexpr uint32_t kTxPerCta = kABytes + kBBytes + kSfBytes;
-#ifdef MXB200_EXP_PARTS2
-  static constexpr int kStages = (TN == 192 ? 7 : 6) - (kFuse == kFuseNone ? 0 : 1);
-#else
   static constexpr int kStages = (TN == 192 ? 7 : 6) - (kFuse == kFuseNone ? 0 : 2);
-#endif
   static constexpr bool kOverlap = TN == 256;
   static constexpr uint32_t kAcc0 = 0, kAcc1 = kOverlap ? 224 : TN;
   static constexpr uint32_t kSfaCol = kOverlap ? 480 : 2 * TN, kSfbCol = kSfaCol + 4;
+  // fused quantizer on the 256-wide tile: a CTA's 128 x 256 half tile is exactly two scale tiles of q and two of q_t
+  // (512 bytes each), assembled in shared memory (one set per accumulator buffer) and written out whole
+  static constexpr bool kStageScales = kFuse != kFuseNone && TN == 256;
+  static constexpr int kScaleStageBytes = kStageScales ? 2 * 4 * kScaleTileBytes : 0;
   static constexpr size_t kSmemBytes = 1024 + static_cast<size_t>(kStages) * (kABytes + kBBytes + kSfBytes) +
-                                       kEpiWarps * kEpiBytes + 512;
+                                       kEpiWarps * kEpiBytes + kScaleStageBytes + 512;
   static_assert(kSmemBytes <= 232448, "shared memory per CTA");
   static_assert(sizeof(Barriers) <= 512, "barrier block");
 };
@@ -909,7 +916,8 @@ __device__ __forceinline__ void pair_kernel_body(const CUtensorMap* map_a, const
   unsigned char* s_b = s_a + C::kStages * C::kABytes;
   unsigned char* s_epi = s_b + C::kStages * C::kBBytes;  // 2 KB per epilogue warp: 32 rows x 64 bytes
   unsigned char* s_sf = s_epi + C::kEpiWarps * C::kEpiBytes;  // per stage: A's tile, B's two tiles
-  Barriers* bars = reinterpret_cast<Barriers*>(s_sf + C::kStages * C::kSfBytes);
+  unsigned char* s_scales = s_sf + C::kStages * C::kSfBytes;  // fused quantizer: [buffer][q tile 0, 1, q_t tile 0, 1][512]
+  Barriers* bars = reinterpret_cast<Barriers*>(s_scales + C::kScaleStageBytes);
 
   const int warp = static_cast<int>(threadIdx.x) >> 5, lane = static_cast<int>(threadIdx.x) & 31;
   const uint32_t rank = cluster_ctarank();
@@ -935,6 +943,7 @@ __device__ __forceinline__ void pair_kernel_body(const CUtensorMap* map_a, const
     }
     bars->abort_flag = 0;
     bars->last_flag = 0;
+    bars->scale_done[0] = bars->scale_done[1] = 0;
     fence_mbar_init();
   }
   if (warp == 0 && lane == 0) {
@@ -1199,7 +1208,8 @@ __device__ __forceinline__ void pair_kernel_body(const CUtensorMap* map_a, const
         } else if constexpr (kFuse != kFuseNone) {
           fused_quantize_chunk<kFuse>(p, map_d, map_q, map_qt, stage, lane, reinterpret_cast<const float*>(r[i & 1]),
                                       row, col, warp_row0, row_ok && col < p.N, h_pieces,
-                                      i + 1 < n_mine ? col0 + chunk_of(i + 1) * 32 : -1);
+                                      i + 1 < n_mine ? col0 + chunk_of(i + 1) * 32 : -1,
+                                      C::kStageScales ? s_scales + buf * (4 * kScaleTileBytes) : nullptr, c);
         } else {
           const bool valid = row_ok && col < p.N;
           const bool issue = warp_row0 < p.M && col < p.N;
@@ -1208,6 +1218,34 @@ __device__ __forceinline__ void pair_kernel_body(const CUtensorMap* map_a, const
           store_rows_tma(map_d, stage, lane, o, col, warp_row0, issue);
           if (p.out_kind == kOutF32)
             store_rows_tma(map_d, stage, lane, o + 16, col + 16, warp_row0, issue);
+        }
+      }
+      if constexpr (C::kStageScales) {
+        // the warp that finishes the half tile last writes its four assembled scale tiles out, 16 bytes per lane and
+        // step; the accumulator buffer (and with it this set of staged tiles) is handed back only after that
+        __syncwarp();
+        uint32_t prev = 0;
+        if (lane == 0) {
+          __threadfence_block();
+          prev = atomicAdd(&bars->scale_done[buf], 1u);
+        }
+        prev = __shfl_sync(0xffffffffu, prev, 0);
+        if (prev == static_cast<uint32_t>(C::kEpiWarps) - 1u) {
+          __threadfence_block();
+          const unsigned char* src = s_scales + buf * (4 * kScaleTileBytes);
+          const int row0 = tc.m * C::kTileM + static_cast<int>(rank) * 128;
+#pragma unroll
+          for (int t = 0; t < 4; ++t) {
+            const int group = (col0 >> 7) + (t & 1);  // 128-column group of the output
+            if (row0 < p.M && group * 128 < p.N) {
+              uint8_t* dst = t < 2 ? p.q_scale + (static_cast<int64_t>(row0 >> 7) * p.q_scale_tiles + group) * kScaleTileBytes
+                                   : p.qt_scale + (static_cast<int64_t>(group) * p.qt_scale_tiles + (row0 >> 7)) * kScaleTileBytes;
+              reinterpret_cast<uint4*>(dst)[lane] = reinterpret_cast<const uint4*>(src + t * kScaleTileBytes)[lane];
+            }
+          }
+          __syncwarp();
+          if (lane == 0)
+            *reinterpret_cast<volatile uint32_t*>(&bars->scale_done[buf]) = 0;
         }
       }
       tcgen05_fence_before_sync();
