@@ -367,7 +367,7 @@ def run_gpu_arm(args):
             "config": {"workload": WORKLOAD, "tflop_per_rank_step": flops / 1e12, "global_tokens": cfg.tokens * world,
                        "parallelism": f"dp{world}", "l2": "operands and outputs of every launch exceed or rotate past the 126 MB L2 (9+ GB touched per step)",
                        "collective": (f"bf16 reduce-scatter (avg) of whole matrices per rank in the reference's stack segments over NCCL "
-                                      f"(max {nccl_max_ctas} CTAs), overlapped with backward") if world > 1 else "none (1 rank)"},
+                                      f"({'NCCL default CTAs' if nccl_max_ctas <= 0 else 'max ' + str(nccl_max_ctas) + ' CTAs'}), overlapped with backward") if world > 1 else "none (1 rank)"},
             "per_gpu_tflops": value / world,
             "pct_of_fp8_spec_peak": 100.0 * value / world / FP8_SPEC_TFLOPS,
             "pct_of_2x_measured_bf16_sustained": 100.0 * value / world / fp8_2x,
