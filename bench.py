@@ -12,7 +12,8 @@ distributions; there is no dataset or checkpoint on this path.
 
 value: GEMM TFLOP/s of the whole job (all ranks), from device time of the timed steps, inputs resident in HBM.
 The steps are then run a second time with CUDA events around every launch, which gives the per-kernel durations.
-e2e: the same with each step's micro-batch activations copied from pinned host memory inside the timed region
+e2e: the same with one full set of every per-step input (activations, residual, incoming gradients, lm_head
+activations and logit gradients: everything but the weights) copied from pinned host memory inside the timed region
 (on a copy stream, one step ahead, as a loader would) and a slice of the result read back every step. roofline: the GEMM kernel alone, bracketed by CUDA events on its stream.
 cpu_baseline / --impl reference: the reference's CPU formulation of the path (libtorch quantize -> dequantize ->
 fp32 matmul, oracle/torch_reference.py) on a bounded sample, on the host cores.
@@ -296,10 +297,13 @@ def run_gpu_arm(args):
         step.cfg.real_producers = False
         watchdog = watchdog or nc.capi.device_status()
 
-    # ---- end to end: every step's micro-batch activations come from pinned host memory and a result slice goes back.
-    # As a training loop's loader would, the copy of step i + 1's inputs runs on a copy stream into staging buffers
-    # while step i computes; the step then takes them with a device-side copy. All of it is inside the timed region.
-    targets = (step.x_attn[0], step.y_att[0], step.x_mlp[0])
+    # ---- end to end: one full set of every per-step input of the path (the activations and residual each Linear
+    # reads, the gradients each backward reads, the lm_head's activations and a chunk of logit gradients; everything but
+    # the weights, which are parameters) comes from pinned host memory and a result slice goes back. As a training
+    # loop's loader would, the copy of step i + 1's inputs runs on a copy stream into staging buffers while step i
+    # computes; the step then takes them with a device-side copy. All of it is inside the timed region.
+    targets = (step.x_attn[0], step.y_att[0], step.x_mlp[0], step.resid[0], step.dy_proj[0], step.dy_o[0], step.dy_qkv[0],
+               step.x_lm, step.dlogits[0])
     host_in = [t.cpu().pin_memory() for t in targets]
     staging = [torch.empty_like(t) for t in targets]
     host_out = torch.empty(4096, dtype=torch.bfloat16).pin_memory()
