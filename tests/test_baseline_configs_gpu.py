@@ -226,3 +226,32 @@ def test_fused_quantize_epilogues_at_d24_size():
     for name in ("data", "inv_scale", "data_t", "inv_scale_t"):
         a, b = getattr(got, name).view(torch.uint8), getattr(want_bwd, name).view(torch.uint8)
         assert torch.equal(a, b), f"relu^2 bwd {name}: {(a != b).sum().item()} bytes differ"
+
+
+@pytest.mark.parametrize("depth", [12, 26])
+def test_d12_and_d26_linear_shapes(depth):
+    """The tile scheduler is sized for d12 to d26 (n_embd = 64 x depth, src/nanochat/model/gpt.cpp:25-39): every Linear
+    shape of the two end points (C = 768 and C = 1664, whose K = 13 x 128 and N = 4992 / 6656 are not multiples of either
+    tile width) forward, dgrad and wgrad at M = 4096 tokens: sampled rows against the oracle's dequantized product,
+    the whole output against cuBLASLt's MXFP8 GEMM on the same operands, and determinism."""
+    C, M = 64 * depth, 4096
+    g = torch.Generator(device="cuda").manual_seed(100 + depth)
+    rows = np.array([0, 127, 128, 2049, M - 1])
+    for name, N, K in (("qkv", 3 * C, C), ("attn_out", C, C), ("mlp_fc", 4 * C, C), ("mlp_proj", C, 4 * C)):
+        x = torch.randn(M, K, device="cuda", generator=g).to(torch.bfloat16)
+        w = (torch.randn(N, K, device="cuda", generator=g) / K ** 0.5).to(torch.bfloat16)
+        dy = (torch.randn(M, N, device="cuda", generator=g) * 1e-3).to(torch.bfloat16)
+        qx, qw, qg = nc.quantize_mx(x), nc.quantize_mx(w), nc.quantize_mx(dy)
+        cases = (("fwd", qx.data, qx.inv_scale, qw.data, qw.inv_scale, torch.bfloat16),
+                 ("dgrad", qg.data, qg.inv_scale, qw.data_t, qw.inv_scale_t, torch.bfloat16),
+                 ("wgrad", qg.data_t, qg.inv_scale_t, qx.data_t, qx.inv_scale_t, torch.float32))
+        for what, a, a_s, b, b_s, dt in cases:
+            y = nc.mx_gemm(a, a_s, b, b_s, dt)
+            assert torch.equal(y, nc.mx_gemm(a, a_s, b, b_s, dt)), (name, what)
+            lt = torch._scaled_mm(a, b.t(), a_s, b_s, None, None, dt, False)
+            assert rel(np_f32(y), np_f32(lt)) < (TOL_BF16 if dt == torch.bfloat16 else TOL_F32), (name, what)
+            r = rows[rows < a.size(0)]
+            da = mo.mx_dequantize(np_u8(a), np_u8(a_s))[r].astype(np.float64)
+            db = mo.mx_dequantize(np_u8(b), np_u8(b_s)).astype(np.float64)
+            tol = TOL_BF16 if dt == torch.bfloat16 else TOL_F32 * 3
+            assert rel(np_f32(y)[r], da @ db.T) < tol, (name, what)
