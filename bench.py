@@ -40,9 +40,9 @@ NCCL_MAX_CTAS = 0  # cap on the CTAs NCCL may use per collective (0: NCCL's defa
                    # or 4 slows the collective more than it frees SMs for the GEMMs it overlaps)
 FP8_SPEC_TFLOPS = 4500.0  # B200 dense FP8, 2x the 2.25e15 bf16 figure
 # dram__bytes_read.sum + dram__bytes_write.sum of one captured launch of the GEMM kernel, the merged-QKV forward
-# (M=16384, N=4608, K=1536, bf16 out), from the ncu summary of the pair kernel kept under profiles/. Its algorithmic
-# bytes: 184.3e6.
-GEMM_TRAFFIC_BYTES = 167.5e6
+# (M=16384, N=4608, K=1536, bf16 out: 45.2 MB read + 100.2 MB written), from the ncu summary of the CTA-pair kernels kept
+# under profiles/ (ncu cannot run inside this benchmark, so the figure is carried here). Its algorithmic bytes: 184.3e6.
+GEMM_TRAFFIC_BYTES = 145.4e6
 GEMM_TRAFFIC_LAUNCH = "qkv.fwd 16384x4608x1536 (algorithmic 184.3 MB; the step's other launches differ in shape)"
 
 
