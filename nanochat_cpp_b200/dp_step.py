@@ -445,6 +445,9 @@ class DpStep:
         wq, b = self.wq[l], self.bucket
         # MLP proj: dA = dY . W, dW = dY^T . A
         self._quant(self.dy_proj[s], self.gq_c)
+        # the reference's order (fp8.cpp:299-337): proj weight gradient, then the dgrad whose epilogue quantizes dh,
+        # then fc's dgrad and weight gradient, which read that dh while it is still in L2
+        self._wgrad(b.matrix(l, 3), self._grad(l, 3), self.gq_c.data_t, self.gq_c.inv_scale_t, self.aq[l].data_t, self.aq[l].inv_scale_t)
         if self.cfg.fused_mlp and not self.gemm_only:
             # dgrad GEMM whose epilogue reads h and emits MX(dh) directly; dA is never written (fp8.cpp:318-323)
             if self.hook:
@@ -465,7 +468,6 @@ class DpStep:
                     nc.SCALE_REFERENCE, torch.cuda.current_stream().cuda_stream), "quantize dh")
             if self.qhook and not self.gemm_only:
                 self.qhook(False)
-        self._wgrad(b.matrix(l, 3), self._grad(l, 3), self.gq_c.data_t, self.gq_c.inv_scale_t, self.aq[l].data_t, self.aq[l].inv_scale_t)
         self._gemm(self.dx, self.gq_4c.data, self.gq_4c.inv_scale, wq[2].data_t, wq[2].inv_scale_t)
         self._wgrad(b.matrix(l, 2), self._grad(l, 2), self.gq_4c.data_t, self.gq_4c.inv_scale_t, self.xq_mlp[l].data_t, self.xq_mlp[l].inv_scale_t)
         # attention out

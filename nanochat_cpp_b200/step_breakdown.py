@@ -22,7 +22,7 @@ def class_labels(cfg: StepConfig, n_weight_launches: int):
     L, chunks = cfg.n_layer, cfg.tokens // cfg.chunk_rows
     fc, pd = ("mlp_fc.fwd+q", "mlp_proj.dgrad+q") if cfg.fused_mlp else ("mlp_fc.fwd", "mlp_proj.dgrad")
     gemm = ["qkv.fwd", "attn_out.fwd", fc, "mlp_proj.fwd"] * L + ["lm_head.fwd", "lm_head.dgrad"] * chunks + ["lm_head.wgrad"]
-    gemm += [pd, "mlp_proj.wgrad", "mlp_fc.dgrad", "mlp_fc.wgrad", "attn_out.dgrad", "attn_out.wgrad", "qkv.dgrad",
+    gemm += ["mlp_proj.wgrad", pd, "mlp_fc.dgrad", "mlp_fc.wgrad", "attn_out.dgrad", "attn_out.wgrad", "qkv.dgrad",
              "qkv.wgrad"] * L
     fwd_q = ["quantize x_attn", "quantize y_att", "quantize x_mlp"] + ([] if cfg.fused_mlp else ["quantize relu2(h)"])
     bwd_q = ["quantize dy_proj"] + ([] if cfg.fused_mlp else ["quantize dh"]) + ["quantize dy_o", "quantize dy_qkv"]
