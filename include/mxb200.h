@@ -64,7 +64,10 @@ typedef struct mxb200_mx_out {
  * nanochat_mx_quantize_{bf16,f32,relu_square_bf16}, fp8_kernel.cu:197-205).
  * x: (rows, cols) contiguous bf16 (x_bf16 != 0) or fp32. out: x scaled along its rows; out_t: x's transpose
  * (cols, rows) scaled along its own rows. rows, cols % 128 == 0 (the callers' mx_fits, fp8.h:86-88);
- * x, data pointers and lds 16-byte aligned. prologue RELU_SQUARE quantizes bf16(relu(x)^2), bf16 x only. */
+ * x, data pointers and lds 16-byte aligned. prologue RELU_SQUARE quantizes bf16(relu(x)^2), bf16 x only.
+ * Plain bf16 tensors of more than four tiles of 128 x 128 per SM run as persistent CTAs that draw their tiles from a
+ * counter in the library's device image; at most 256 such launches may be in flight on a device at once (launches on
+ * one stream never overlap; this bounds launches spread over many streams). */
 MXB200_API int mxb200_quantize_mx(const void* x, int x_bf16, int64_t rows, int64_t cols, mxb200_mx_out out, mxb200_mx_out out_t,
                        int prologue, int scale_rule, void* stream);
 
@@ -209,9 +212,9 @@ MXB200_API int mxb200_gemm_splitk_static(const void* a, const void* a_scale, con
 /* Static message for a status (the reference's seam returns const char* messages, mx_gemm_kernel.h:12). */
 MXB200_API const char* mxb200_strerror(int status);
 
-/* Every device-side wait in the GEMM is bounded; a wait that runs out records where in a device word and the
- * kernel returns instead of spinning. This reads that word for the current device (0 = none) and clears it.
- * Synchronises the device. */
+/* Every device-side wait (GEMM, fused residual step, streaming quantizer) is bounded; a wait that runs out records
+ * where in a device word and the kernel returns instead of spinning. This reads that word for the current device
+ * (0 = none) and clears it. Synchronises the device. */
 MXB200_API int mxb200_device_status(uint32_t* word);
 
 /* Exercises that path without a stuck kernel: launches one warp that waits, with the given limit, on a barrier nothing

@@ -68,6 +68,40 @@ __device__ __forceinline__ uint32_t e4m3x4_scaled(uint32_t w0, uint32_t w1, uint
   return e4m3x4_from_f32(lo_f32(a), hi_f32(a), lo_f32(b), hi_f32(b));
 }
 
+// The same through the mixed-precision multiply-add (fp32 = bf16 * bf16 + fp32): the halves feed the multiplier
+// as 16-bit operands, so no instruction is spent widening them. mlo and mhi are the bf16 bits of the multipliers of
+// the low and the high halves. The addend is -0, which keeps the sign of a zero product.
+__device__ __forceinline__ uint32_t e4m3x4_scaled_fma(uint32_t w0, uint32_t w1, uint16_t mlo, uint16_t mhi) {
+  uint32_t d;
+  asm("{\n\t.reg .b16 a0, a1, b0, b1, lo, hi;\n\t.reg .f32 f0, f1, f2, f3;\n\t"
+      "mov.b32 {a0, a1}, %1;\n\tmov.b32 {b0, b1}, %2;\n\t"
+      "fma.rn.f32.bf16 f0, a0, %3, 0f80000000;\n\tfma.rn.f32.bf16 f1, a1, %4, 0f80000000;\n\t"
+      "fma.rn.f32.bf16 f2, b0, %3, 0f80000000;\n\tfma.rn.f32.bf16 f3, b1, %4, 0f80000000;\n\t"
+      "cvt.rn.satfinite.e4m3x2.f32 lo, f1, f0;\n\tcvt.rn.satfinite.e4m3x2.f32 hi, f3, f2;\n\t"
+      "mov.b32 %0, {lo, hi};\n\t}\n"
+      : "=r"(d)
+      : "r"(w0), "r"(w1), "h"(mlo), "h"(mhi));
+  return d;
+}
+
+// Four packed words holding two interleaved series (low halves, high halves): the e4m3 of the four low halves times
+// mlo and of the four high halves times mhi, each as one word.
+__device__ __forceinline__ void e4m3x4_scaled_fma_split(uint32_t w0, uint32_t w1, uint32_t w2, uint32_t w3, uint16_t mlo,
+                                                        uint16_t mhi, uint32_t& out_lo, uint32_t& out_hi) {
+  asm("{\n\t.reg .b16 a0, a1, b0, b1, c0, c1, d0, d1, p, q;\n\t.reg .f32 f0, f1, f2, f3;\n\t"
+      "mov.b32 {a0, a1}, %2;\n\tmov.b32 {b0, b1}, %3;\n\tmov.b32 {c0, c1}, %4;\n\tmov.b32 {d0, d1}, %5;\n\t"
+      "fma.rn.f32.bf16 f0, a0, %6, 0f80000000;\n\tfma.rn.f32.bf16 f1, b0, %6, 0f80000000;\n\t"
+      "fma.rn.f32.bf16 f2, c0, %6, 0f80000000;\n\tfma.rn.f32.bf16 f3, d0, %6, 0f80000000;\n\t"
+      "cvt.rn.satfinite.e4m3x2.f32 p, f1, f0;\n\tcvt.rn.satfinite.e4m3x2.f32 q, f3, f2;\n\t"
+      "mov.b32 %0, {p, q};\n\t"
+      "fma.rn.f32.bf16 f0, a1, %7, 0f80000000;\n\tfma.rn.f32.bf16 f1, b1, %7, 0f80000000;\n\t"
+      "fma.rn.f32.bf16 f2, c1, %7, 0f80000000;\n\tfma.rn.f32.bf16 f3, d1, %7, 0f80000000;\n\t"
+      "cvt.rn.satfinite.e4m3x2.f32 p, f1, f0;\n\tcvt.rn.satfinite.e4m3x2.f32 q, f3, f2;\n\t"
+      "mov.b32 %1, {p, q};\n\t}\n"
+      : "=&r"(out_lo), "=&r"(out_hi)
+      : "r"(w0), "r"(w1), "r"(w2), "r"(w3), "h"(mlo), "h"(mhi));
+}
+
 // Running maximum of |x| over packed bf16 that skips NaN as fmaxf does (a NaN operand returns the other one), one
 // instruction per word. The result's sign bits carry no meaning (xor of the operands' signs): mask them off at the end.
 __device__ __forceinline__ uint32_t max_abs_skip_nan_bf16x2(uint32_t m, uint32_t w) {

@@ -664,16 +664,18 @@ __device__ __forceinline__ void load_h_pieces(const GemmParams& p, int lane, int
 // Quantizes one scale block held as 16 packed words (32 bf16 in block order) into 32 e4m3 bytes w[8]; returns the
 // block's biased exponent.
 __device__ __forceinline__ int quantize_block(const uint32_t* v, int floor_rule, uint32_t* w) {
-  uint32_t m = 0u;  // NaN operands are skipped, as by the quantizer's fmaxf
+  // NaN operands are skipped, as by the quantizer's fmaxf; four running maxima keep the dependent chain short
+  uint32_t m4[4] = {0u, 0u, 0u, 0u};
 #pragma unroll
   for (int k = 0; k < 16; ++k)
-    m = max_abs_skip_nan_bf16x2(m, v[k]);
+    m4[k & 3] = max_abs_skip_nan_bf16x2(m4[k & 3], v[k]);
+  uint32_t m = max_abs_skip_nan_bf16x2(max_abs_skip_nan_bf16x2(m4[0], m4[1]), max_abs_skip_nan_bf16x2(m4[2], m4[3]));
   m &= 0x7fff7fffu;
   const int e = mx_exponent(max(m & 0xffffu, m >> 16) << 16, floor_rule);
-  const uint32_t mul2 = (mx_multiplier_bits(e) >> 16) * 0x10001u;
+  const uint16_t mb = static_cast<uint16_t>(mx_multiplier_bits(e) >> 16);
 #pragma unroll
   for (int k = 0; k < 8; ++k)
-    w[k] = e4m3x4_scaled(v[2 * k], v[2 * k + 1], mul2);
+    w[k] = e4m3x4_scaled_fma(v[2 * k], v[2 * k + 1], mb, mb);
   return e;
 }
 
@@ -1813,6 +1815,8 @@ extern "C" int mxb200_device_status(uint32_t* word) {
   }
   if (const uint32_t norm = mxb200::take_norm_watchdog_word(); w == 0)
     w = norm;
+  if (const uint32_t quant = mxb200::take_quantize_watchdog_word(); w == 0)
+    w = quant;
   if (word != nullptr)
     *word = w;
   return w == 0 ? MXB200_OK : MXB200_ERR_WATCHDOG;

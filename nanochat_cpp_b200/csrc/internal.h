@@ -31,6 +31,8 @@ EncodeTiledFn encode_fn();
 
 // The residual-norm kernel's watchdog word (non-zero after one of its bounded waits ran out), read and cleared.
 uint32_t take_norm_watchdog_word();
+// The same for the streaming quantizer.
+uint32_t take_quantize_watchdog_word();
 
 inline bool aligned16(const void* p) {
   return (reinterpret_cast<uintptr_t>(p) & 15u) == 0;

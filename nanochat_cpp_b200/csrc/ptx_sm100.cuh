@@ -103,6 +103,17 @@ __device__ __forceinline__ void tma_load_2d(uint32_t pred, void* smem_dst, const
         : "memory");
 }
 
+// The same load with an L2 eviction-priority hint (a createpolicy value), for data that is read once.
+__device__ __forceinline__ void tma_load_2d_hint(uint32_t pred, void* smem_dst, const CUtensorMap* map, uint64_t* bar,
+                                                 int32_t x, int32_t y, uint64_t policy) {
+  asm volatile(
+        "{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %5, 0;\n\t"
+        "@q cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4}], [%2], %6;\n\t}\n"
+        ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(pred),
+          "l"(policy)
+        : "memory");
+}
+
 // Untiled bulk copy global -> shared: both addresses 16-byte aligned, bytes % 16 == 0.
 __device__ __forceinline__ void bulk_load(uint32_t pred, void* smem_dst, const void* gmem_src, uint32_t bytes,
                                           uint64_t* bar) {

@@ -2,23 +2,29 @@
 // (transposed) in one pass over the input. Replaces nanochat-cpp's nanochat_mx_quantize_* kernels
 // (src/nanochat/model/fp8/fp8_kernel.cu:197-210, body mx_kernel.cuh:72-107); same bytes, different schedule.
 //
-// One CTA owns a 128 x 128 tile, which is exactly one 512-byte swizzled scale tile in each layout.
-//   row pass:    each thread loads 16 consecutive values with 256-bit loads (one for bf16, two for fp32), fully
-//                coalesced; the block maximum of 32 values is a 2-lane shuffle (for plain bf16 input the
-//                per-thread maximum and the multiply by the power-of-two scale stay packed bf16x2); 16 E4M3 bytes leave with one
-//                128-bit store (a warp writes 512 contiguous bytes). The loaded values are parked in shared
-//                memory in their input type (prologue values are bf16-exact).
+// The unit of work is a 128 x 128 tile, which is exactly one 512-byte swizzled scale tile in each layout.
+//   row pass:    each thread takes 16 consecutive values (256-bit loads, one for bf16, two for fp32, fully
+//                coalesced); the block maximum of 32 values is a 2-lane shuffle (for plain bf16 input the per-thread
+//                maximum stays packed bf16x2 and the multiply by the power-of-two scale is the mixed-precision
+//                fp32 = bf16 * bf16 multiply-add, which takes the 16-bit halves as they are); 16 E4M3 bytes leave
+//                with one 128-bit store (a warp writes 512 contiguous bytes). The loaded values are parked in
+//                shared memory in their input type (prologue values are bf16-exact).
 //   column pass: each thread owns two adjacent columns x 32 rows, read from shared memory as packed pairs
 //                (a warp reads 128 contiguous bytes per row, conflict-free), needs no shuffle, and writes
 //                32 contiguous bytes of each transposed row with one 256-bit store (a full DRAM sector).
 //   scales:      staged in shared memory in swizzled order and written as 16-byte vectors, 512 bytes per tile.
+// Two schedules: one CTA per tile (every input type and prologue; tensors of up to one wave), and for plain bf16
+// tensors of more than one wave persistent CTAs that draw tiles from a counter and bring them in by TMA a tile ahead.
 // HBM traffic is the algorithmic minimum: every input byte read once, every output byte written once.
+#include <algorithm>
+
 #include <cuda_bf16.h>
 #include <cuda_fp8.h>
 
 #include "bf16x2_sm100.cuh"
 #include "internal.h"
 #include "mx_common.cuh"
+#include "ptx_sm100.cuh"
 
 namespace mxb200 {
 
@@ -118,6 +124,75 @@ __device__ __forceinline__ void load_u32x8_stream(const void* p, uint32_t (&w)[8
   }
 }
 
+// Column pass over a parked 128 x 128 tile: thread = (column pair, 32-row block); reads packed pairs (a warp reads 128
+// contiguous bytes per row), writes 32 contiguous bytes of each transposed row and stages the two scale bytes.
+template <bool kIn32>
+__device__ __forceinline__ void column_pass(const typename std::conditional<kIn32, float, __nv_bfloat16>::type* tile,
+                                            const QuantParams& p, int64_t row0, int64_t col0, unsigned char* sc_cols,
+                                            int t) {
+  const int cp = t & 63, rb = t >> 6;
+  uint32_t wlo[8], whi[8];
+  int elo, ehi;
+  if constexpr (kIn32) {
+    float lo[32], hi[32];
+    float mlo = 0.f, mhi = 0.f;
+#pragma unroll
+    for (int k = 0; k < 32; ++k) {
+      const float2 f = *reinterpret_cast<const float2*>(tile + (rb * 32 + k) * kTile + 2 * cp);
+      lo[k] = f.x, hi[k] = f.y;
+      mlo = fmaxf(mlo, fabsf(lo[k]));
+      mhi = fmaxf(mhi, fabsf(hi[k]));
+    }
+    elo = mx_exponent(__float_as_uint(mlo), p.floor_rule), ehi = mx_exponent(__float_as_uint(mhi), p.floor_rule);
+    const float mullo = __uint_as_float(mx_multiplier_bits(elo)), mulhi = __uint_as_float(mx_multiplier_bits(ehi));
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      wlo[k] = cvt_e4m3x4(lo[4 * k] * mullo, lo[4 * k + 1] * mullo, lo[4 * k + 2] * mullo, lo[4 * k + 3] * mullo);
+      whi[k] = cvt_e4m3x4(hi[4 * k] * mulhi, hi[4 * k + 1] * mulhi, hi[4 * k + 2] * mulhi, hi[4 * k + 3] * mulhi);
+    }
+  } else {
+    // the two columns stay packed as bf16 pairs: 32 registers instead of 64, absmax on the 16-bit patterns
+    uint32_t w[32];
+#pragma unroll
+    for (int k = 0; k < 32; ++k)
+      w[k] = *reinterpret_cast<const uint32_t*>(tile + (rb * 32 + k) * kTile + 2 * cp);
+    // four running maxima, so that the chain of dependent instructions is 8 + 2 long instead of 32
+    uint32_t m4[4] = {0u, 0u, 0u, 0u};
+#pragma unroll
+    for (int k = 0; k < 32; ++k)
+      m4[k & 3] = max_abs_skip_nan_bf16x2(m4[k & 3], w[k]);
+    uint32_t m = max_abs_skip_nan_bf16x2(max_abs_skip_nan_bf16x2(m4[0], m4[1]), max_abs_skip_nan_bf16x2(m4[2], m4[3]));
+    m &= 0x7fff7fffu;
+    elo = mx_exponent((m & 0xffffu) << 16, p.floor_rule), ehi = mx_exponent(m & 0xffff0000u, p.floor_rule);
+    const uint16_t mlo = static_cast<uint16_t>(mx_multiplier_bits(elo) >> 16), mhi = static_cast<uint16_t>(mx_multiplier_bits(ehi) >> 16);
+#pragma unroll
+    for (int k = 0; k < 8; ++k)
+      e4m3x4_scaled_fma_split(w[4 * k], w[4 * k + 1], w[4 * k + 2], w[4 * k + 3], mlo, mhi, wlo[k], whi[k]);
+  }
+  unsigned char* dst = static_cast<unsigned char*>(p.out_t.data) + (col0 + 2 * cp) * p.out_t.ld + row0 + rb * 32;
+  store_u32x8(dst, wlo, p.wide_out_t);
+  store_u32x8(dst + p.out_t.ld, whi, p.wide_out_t);
+  sc_cols[mx_scale_tile_offset(2 * cp, rb)] = static_cast<unsigned char>(elo);
+  sc_cols[mx_scale_tile_offset(2 * cp + 1, rb)] = static_cast<unsigned char>(ehi);
+}
+
+// One 512-byte scale tile per layout leaves shared memory as 16-byte vectors (threads 0-31 rows, 32-63 columns).
+__device__ __forceinline__ void write_scale_tiles(const QuantParams& p, int tile_r, int tile_c, const unsigned char* sc_rows,
+                                                  const unsigned char* sc_cols, int t) {
+  const bool want_rows = p.out.data != nullptr, want_cols = p.out_t.data != nullptr;
+  if (t < 32) {
+    if (want_rows)
+      reinterpret_cast<uint4*>(static_cast<unsigned char*>(p.out.scale) +
+                               (static_cast<int64_t>(tile_r) * p.out.scale_tiles + tile_c) * kScaleTileBytes)[t] =
+            reinterpret_cast<const uint4*>(sc_rows)[t];
+  } else if (t < 64) {
+    if (want_cols)
+      reinterpret_cast<uint4*>(static_cast<unsigned char*>(p.out_t.scale) +
+                               (static_cast<int64_t>(tile_c) * p.out_t.scale_tiles + tile_r) * kScaleTileBytes)[t - 32] =
+            reinterpret_cast<const uint4*>(sc_cols)[t - 32];
+  }
+}
+
 // kIn32: fp32 input (parked as float), else bf16 (parked as bf16).
 // Row pass: a thread owns 16 consecutive values of a row (one 256-bit load of bf16), two lanes share a 32-value
 // block (one shuffle), 16 E4M3 bytes leave with one 128-bit store (512 contiguous bytes per warp).
@@ -125,7 +200,7 @@ __device__ __forceinline__ void load_u32x8_stream(const void* p, uint32_t (&w)[8
 template <bool kIn32, int kPro>
 __device__ __forceinline__ void quantize_tile(const QuantParams& p, int tile_index) {
   using Park = typename std::conditional<kIn32, float, __nv_bfloat16>::type;
-  extern __shared__ __align__(16) unsigned char smem_raw[];
+  extern __shared__ __align__(128) unsigned char smem_raw[];
   Park* tile = reinterpret_cast<Park*>(smem_raw);                               // [128][128]
   unsigned char* sc_rows = smem_raw + sizeof(Park) * kTile * kTile;             // 512 B, swizzled
   unsigned char* sc_cols = sc_rows + kScaleTileBytes;                           // 512 B, swizzled
@@ -251,11 +326,11 @@ __device__ __forceinline__ void quantize_tile(const QuantParams& p, int tile_ind
       uint4 o;
       if constexpr (!kIn32 && kPro == kNone) {
         // the multiplier is a power of two: the packed bf16 product is exact wherever e4m3 can tell
-        const uint32_t mul2 = (mx_multiplier_bits(e) >> 16) * 0x10001u;
-        o.x = e4m3x4_scaled(raw[it][0], raw[it][1], mul2);
-        o.y = e4m3x4_scaled(raw[it][2], raw[it][3], mul2);
-        o.z = e4m3x4_scaled(raw[it][4], raw[it][5], mul2);
-        o.w = e4m3x4_scaled(raw[it][6], raw[it][7], mul2);
+        const uint16_t mb = static_cast<uint16_t>(mx_multiplier_bits(e) >> 16);
+        o.x = e4m3x4_scaled_fma(raw[it][0], raw[it][1], mb, mb);
+        o.y = e4m3x4_scaled_fma(raw[it][2], raw[it][3], mb, mb);
+        o.z = e4m3x4_scaled_fma(raw[it][4], raw[it][5], mb, mb);
+        o.w = e4m3x4_scaled_fma(raw[it][6], raw[it][7], mb, mb);
       } else {
         const float mul = __uint_as_float(mx_multiplier_bits(e));
         o.x = cvt_e4m3x4(v[0] * mul, v[1] * mul, v[2] * mul, v[3] * mul);
@@ -270,70 +345,191 @@ __device__ __forceinline__ void quantize_tile(const QuantParams& p, int tile_ind
   }
   __syncthreads();
 
-  // ---- column pass: thread = (column pair, 32-row block)
+  // ---- column pass, then the scales
   if (want_cols) {
-    const int cp = t & 63, rb = t >> 6;
-    uint32_t wlo[8], whi[8];
-    int elo, ehi;
-    if constexpr (kIn32) {
-      float lo[32], hi[32];
-      float mlo = 0.f, mhi = 0.f;
-#pragma unroll
-      for (int k = 0; k < 32; ++k) {
-        const float2 f = *reinterpret_cast<const float2*>(tile + (rb * 32 + k) * kTile + 2 * cp);
-        lo[k] = f.x, hi[k] = f.y;
-        mlo = fmaxf(mlo, fabsf(lo[k]));
-        mhi = fmaxf(mhi, fabsf(hi[k]));
-      }
-      elo = mx_exponent(__float_as_uint(mlo), p.floor_rule), ehi = mx_exponent(__float_as_uint(mhi), p.floor_rule);
-      const float mullo = __uint_as_float(mx_multiplier_bits(elo)), mulhi = __uint_as_float(mx_multiplier_bits(ehi));
-#pragma unroll
-      for (int k = 0; k < 8; ++k) {
-        wlo[k] = cvt_e4m3x4(lo[4 * k] * mullo, lo[4 * k + 1] * mullo, lo[4 * k + 2] * mullo, lo[4 * k + 3] * mullo);
-        whi[k] = cvt_e4m3x4(hi[4 * k] * mulhi, hi[4 * k + 1] * mulhi, hi[4 * k + 2] * mulhi, hi[4 * k + 3] * mulhi);
-      }
-    } else {
-      // the two columns stay packed as bf16 pairs: 32 registers instead of 64, absmax on the 16-bit patterns
-      uint32_t w[32];
-#pragma unroll
-      for (int k = 0; k < 32; ++k)
-        w[k] = *reinterpret_cast<const uint32_t*>(tile + (rb * 32 + k) * kTile + 2 * cp);
-      uint32_t m = 0u;
-#pragma unroll
-      for (int k = 0; k < 32; ++k)
-        m = max_abs_skip_nan_bf16x2(m, w[k]);
-      m &= 0x7fff7fffu;
-      elo = mx_exponent((m & 0xffffu) << 16, p.floor_rule), ehi = mx_exponent(m & 0xffff0000u, p.floor_rule);
-      // both columns scaled at once: powers of two, so the packed bf16 products are exact wherever e4m3 can tell
-      const uint32_t mul2 = (mx_multiplier_bits(elo) >> 16) | (mx_multiplier_bits(ehi) & 0xffff0000u);
-#pragma unroll
-      for (int k = 0; k < 32; ++k)
-        w[k] = mul_bf16x2(w[k], mul2);
-#pragma unroll
-      for (int k = 0; k < 8; ++k) {
-        wlo[k] = cvt_e4m3x4(lo_f32(w[4 * k]), lo_f32(w[4 * k + 1]), lo_f32(w[4 * k + 2]), lo_f32(w[4 * k + 3]));
-        whi[k] = cvt_e4m3x4(hi_f32(w[4 * k]), hi_f32(w[4 * k + 1]), hi_f32(w[4 * k + 2]), hi_f32(w[4 * k + 3]));
-      }
-    }
-    unsigned char* dst = static_cast<unsigned char*>(p.out_t.data) + (col0 + 2 * cp) * p.out_t.ld + row0 + rb * 32;
-    store_u32x8(dst, wlo, p.wide_out_t);
-    store_u32x8(dst + p.out_t.ld, whi, p.wide_out_t);
-    sc_cols[mx_scale_tile_offset(2 * cp, rb)] = static_cast<unsigned char>(elo);
-    sc_cols[mx_scale_tile_offset(2 * cp + 1, rb)] = static_cast<unsigned char>(ehi);
+    column_pass<kIn32>(tile, p, row0, col0, sc_cols, t);
     __syncthreads();
   }
+  write_scale_tiles(p, tile_r, tile_c, sc_rows, sc_cols, t);
+}
 
-  // ---- scales: one 512-byte tile per layout, 16 bytes per thread
-  if (t < 32) {
-    if (want_rows)
-      reinterpret_cast<uint4*>(static_cast<unsigned char*>(p.out.scale) +
-                               (static_cast<int64_t>(tile_r) * p.out.scale_tiles + tile_c) * kScaleTileBytes)[t] =
-            reinterpret_cast<const uint4*>(sc_rows)[t];
-  } else if (t < 64) {
-    if (want_cols)
-      reinterpret_cast<uint4*>(static_cast<unsigned char*>(p.out_t.scale) +
-                               (static_cast<int64_t>(tile_c) * p.out_t.scale_tiles + tile_r) * kScaleTileBytes)[t - 32] =
-            reinterpret_cast<const uint4*>(sc_cols)[t - 32];
+// ---- streaming form for plain bf16 input: persistent CTAs, tiles drawn from a counter and brought in by TMA
+//
+// The one-shot kernel above holds a tile's loads in registers, so a CTA reads, computes and writes in turn and only
+// the other CTAs of its SM overlap with it. Here three CTAs per SM each keep two 32 KB tile buffers: while all threads
+// work on one tile out of shared memory (no load or store instruction is spent on the input), the tiled TMA load of
+// the next is in flight, marked evict-first in L2 because the input is read once. Tiles are handed out by a counter
+// and not by a fixed stride: the CTAs of one SM advance at very different rates (with a fixed stride the first CTA of
+// a 6144-tile tensor was done after 32 us and the last after 81), so a fixed share per CTA leaves most of the machine
+// waiting for the slowest. Inside the benchmark step this form takes 27.5 us for a 16384 x 1536 activation and 61 us
+// for the 16384 x 4608 gradient of the merged QKV, against 28.3 and 66.7 us for the one-shot kernel.
+constexpr int kStreamStages = 2;
+#define MXB200_STREAM_CTAS_PER_SM 3  // also the kernel's launch bound
+constexpr int kStreamCtasPerSm = MXB200_STREAM_CTAS_PER_SM;
+constexpr uint32_t kStreamTileBytes = kTile * kTile * 2;
+constexpr uint64_t kStreamWaitLimitNs = 2000000000ull;
+constexpr uint64_t kStreamDrainLimitNs = 50000000ull;
+
+struct StreamBarriers {
+  uint64_t full[kStreamStages];
+  int tile_of[kStreamStages];  // the tile whose load completes full[s]; -1 is the stop sign
+  uint32_t abort_flag;
+};
+
+// One pair of words per launch in flight, taken round-robin: the next tile to hand out and the CTAs that have left.
+constexpr int kStreamSchedSlots = 256;
+
+constexpr size_t kStreamSmemBytes = kStreamStages * kStreamTileBytes + 4 * kScaleTileBytes + sizeof(StreamBarriers);
+
+}  // namespace
+
+// Non-zero after a bounded wait of the streaming quantizer ran out: 0x40000000 | CTA << 8 | tile in the CTA's walk.
+__device__ uint32_t g_quantize_watchdog_word;
+__device__ uint32_t g_quantize_sched[2 * kStreamSchedSlots];
+
+namespace {
+
+__device__ __forceinline__ bool stream_wait(uint64_t* bar, uint32_t parity, StreamBarriers* bars, uint64_t limit_ns,
+                                            uint32_t site) {
+  if (mbar_try_wait(bar, parity))
+    return true;
+  const uint64_t t0 = global_timer_ns();
+  uint32_t spins = 0;
+  while (!mbar_try_wait(bar, parity)) {
+    if ((++spins & 63u) == 0) {
+      if (*reinterpret_cast<volatile uint32_t*>(&bars->abort_flag) != 0)
+        return false;
+      if (global_timer_ns() - t0 > limit_ns) {
+        *reinterpret_cast<volatile uint32_t*>(&bars->abort_flag) = 1;
+        atomicCAS(&g_quantize_watchdog_word, 0u, 0x40000000u | (blockIdx.x << 8) | (site & 0xffu));
+        return false;
+      }
+    }
+  }
+  return true;
+}
+
+// Row pass from a tile in shared memory. A thread owns 16 consecutive values (32 bytes) and reads them as two 16-byte
+// vectors; lanes 4-7 of every eight take the upper vector first, so the eight lanes of a request cover all 32 banks.
+__device__ __forceinline__ void stream_row_pass(const __nv_bfloat16* tile, const QuantParams& p, int64_t row0,
+                                                int64_t col0, unsigned char* sc_rows, int t) {
+  constexpr int kIters = kTile * (kTile / 16) / kThreads;
+#pragma unroll
+  for (int it = 0; it < kIters; ++it) {
+    const int q = it * kThreads + t, r = q >> 3, piece = q & 7, c = piece * 16;
+    const int swap = piece >> 2;
+    const uint4* src = reinterpret_cast<const uint4*>(tile + r * kTile + c);
+    const uint4 a = src[swap], b = src[swap ^ 1];
+    uint32_t m = max_abs_skip_nan_bf16x2(
+          max_abs_skip_nan_bf16x2(max_abs_skip_nan_bf16x2(a.x, a.y), max_abs_skip_nan_bf16x2(a.z, a.w)),
+          max_abs_skip_nan_bf16x2(max_abs_skip_nan_bf16x2(b.x, b.y), max_abs_skip_nan_bf16x2(b.z, b.w)));
+    m = max_abs_skip_nan_bf16x2(m, 0u);  // a lone NaN operand gives way to the zero, as in a running maximum from 0
+    m &= 0x7fff7fffu;
+    uint32_t m_bits = max(m & 0xffffu, m >> 16) << 16;
+    m_bits = max(m_bits, __shfl_xor_sync(0xffffffffu, m_bits, 1));
+    const int e = mx_exponent(m_bits, p.floor_rule);
+    const uint16_t mb = static_cast<uint16_t>(mx_multiplier_bits(e) >> 16);
+    const uint32_t a0 = e4m3x4_scaled_fma(a.x, a.y, mb, mb), a1 = e4m3x4_scaled_fma(a.z, a.w, mb, mb);
+    const uint32_t b0 = e4m3x4_scaled_fma(b.x, b.y, mb, mb), b1 = e4m3x4_scaled_fma(b.z, b.w, mb, mb);
+    const uint4 o = swap ? make_uint4(b0, b1, a0, a1) : make_uint4(a0, a1, b0, b1);
+    *reinterpret_cast<uint4*>(static_cast<unsigned char*>(p.out.data) + (row0 + r) * p.out.ld + col0 + c) = o;
+    if ((t & 1) == 0)
+      sc_rows[mx_scale_tile_offset(r, c >> 5)] = static_cast<unsigned char>(e);
+  }
+}
+
+struct StreamParams {
+  QuantParams q;
+  int tiles;
+  int slot;
+};
+
+__device__ __forceinline__ void quantize_stream(const CUtensorMap* map_x, const StreamParams& sp) {
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  unsigned char* sc = smem_raw + kStreamStages * kStreamTileBytes;  // [2 tiles in turn][rows, columns][512]
+  StreamBarriers* bars = reinterpret_cast<StreamBarriers*>(sc + 4 * kScaleTileBytes);
+  const QuantParams& p = sp.q;
+  const int t = static_cast<int>(threadIdx.x);
+  const bool want_rows = p.out.data != nullptr, want_cols = p.out_t.data != nullptr;
+  uint32_t* sched = g_quantize_sched + 2 * sp.slot;  // [0] next tile to hand out, [1] CTAs that have left
+
+  if (t == 0) {
+    for (int s = 0; s < kStreamStages; ++s)
+      mbar_init(&bars->full[s], 1);
+    bars->abort_flag = 0;
+    fence_mbar_init();
+  }
+  __syncthreads();
+
+  // Thread 0 posts this CTA's i-th tile and starts its load into buffer i % stages. A number past the last tile is the
+  // stop sign: posted once (a bare arrival completes the phase), after which nothing more is drawn or posted.
+  // The first `stages` tiles of a CTA are fixed (blockIdx.x + i * gridDim.x), so no load at the start waits for an
+  // atomic; the launch's counter hands out the tiles from stages * gridDim.x on, and each draw is issued a whole tile
+  // before its number is needed.
+  bool drawing = true;
+  auto post = [&](int i, int tile) {
+    const int s = i % kStreamStages;
+    if (tile >= sp.tiles) {
+      bars->tile_of[s] = -1;
+      mbar_arrive(&bars->full[s]);
+      drawing = false;
+      return;
+    }
+    bars->tile_of[s] = tile;
+    mbar_arrive_expect_tx(1u, &bars->full[s], kStreamTileBytes);
+    tma_load_2d_hint(1u, smem_raw + s * kStreamTileBytes, map_x, &bars->full[s], (tile % p.tiles_c) * kTile,
+                     (tile / p.tiles_c) * kTile, l2_policy_evict_first());
+  };
+  if (t == 0)
+    for (int i = 0; i < kStreamStages && drawing; ++i)
+      post(i, static_cast<int>(blockIdx.x + i * gridDim.x));
+
+  int i = 0;
+  for (;; ++i) {
+    const int s = i % kStreamStages;
+    int drawn = 0;  // thread 0: the tile of iteration i + stages, asked for now and posted after this tile
+    if (t == 0 && drawing)
+      drawn = static_cast<int>(kStreamStages * gridDim.x + atomicAdd(&sched[0], 1u));
+    const bool landed = stream_wait(&bars->full[s], static_cast<uint32_t>(i / kStreamStages) & 1u, bars,
+                                    kStreamWaitLimitNs, static_cast<uint32_t>(i));
+    const int tile = landed ? *reinterpret_cast<volatile int*>(&bars->tile_of[s]) : -1;
+    const int tile_r = tile / p.tiles_c, tile_c = tile % p.tiles_c;
+    const int64_t row0 = static_cast<int64_t>(tile_r) * kTile, col0 = static_cast<int64_t>(tile_c) * kTile;
+    const __nv_bfloat16* buf = reinterpret_cast<const __nv_bfloat16*>(smem_raw + s * kStreamTileBytes);
+    unsigned char* sc_rows = sc + (i & 1) * 2 * kScaleTileBytes;
+    unsigned char* sc_cols = sc_rows + kScaleTileBytes;
+    if (tile >= 0) {
+      if (want_rows)
+        stream_row_pass(buf, p, row0, col0, sc_rows, t);
+      if (want_cols)
+        column_pass<false>(buf, p, row0, col0, sc_cols, t);
+    }
+    // every thread is done with the buffer and the scale bytes are staged; the stop sign, or a wait that gave up,
+    // ends the walk for all threads together
+    if (__syncthreads_and(tile >= 0) == 0)
+      break;
+    if (t == 0 && drawing)
+      post(i + kStreamStages, drawn);
+    // the next tile stages its scale bytes in the other half, and the one after that comes after another barrier
+    write_scale_tiles(p, tile_r, tile_c, sc_rows, sc_cols, t);
+  }
+  if (t == 0) {
+    if (*reinterpret_cast<volatile uint32_t*>(&bars->abort_flag) != 0) {
+      // loads drawn and not taken may still land in this CTA's shared memory: give them a bounded time before leaving
+      for (int j = i; j < i + kStreamStages; ++j) {
+        const uint64_t t0 = global_timer_ns();
+        while (!mbar_try_wait(&bars->full[j % kStreamStages], static_cast<uint32_t>(j / kStreamStages) & 1u))
+          if (global_timer_ns() - t0 > kStreamDrainLimitNs)
+            break;
+      }
+    }
+    // the last CTA to leave hands the slot back zeroed
+    __threadfence();
+    if (atomicAdd(&sched[1], 1u) == gridDim.x - 1) {
+      sched[0] = 0u;
+      sched[1] = 0u;
+      __threadfence();
+    }
   }
 }
 
@@ -390,6 +586,11 @@ MXB200_QUANTIZE_KERNEL(mxb200_quantize_f32, true, mxb200::kNone, 2)
 MXB200_QUANTIZE_KERNEL(mxb200_quantize_relu_square, false, mxb200::kReluSquare, 4)
 MXB200_QUANTIZE_KERNEL(mxb200_quantize_relu_square_bwd, false, mxb200::kReluSquareBwd, 3)
 MXB200_QUANTIZE_KERNEL(mxb200_quantize_softcap_grad, false, mxb200::kSoftcapGrad, 2)
+// Streaming form: persistent, three CTAs per SM, each with two 32 KB tile buffers.
+__global__ void __launch_bounds__(mxb200::kThreads, MXB200_STREAM_CTAS_PER_SM)
+    mxb200_quantize_bf16_stream(const __grid_constant__ CUtensorMap map_x, const mxb200::StreamParams sp) {
+  mxb200::quantize_stream(&map_x, sp);
+}
 MXB200_QUANTIZE_BATCH_KERNEL(mxb200_quantize_batch_bf16, false, 4)
 MXB200_QUANTIZE_BATCH_KERNEL(mxb200_quantize_batch_f32, true, 2)
 
@@ -447,6 +648,37 @@ int launch(const QuantParams& p, int64_t tiles, cudaStream_t stream) {
   return launch_status();
 }
 
+// The streaming kernel on a plain bf16 tensor: (rows, ld) row-major behind a tiled map with a 128 x 128 box.
+int launch_stream(const QuantParams& p, int64_t rows, int64_t cols, int64_t tiles, int sms, cudaStream_t stream) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr)
+    return MXB200_ERR_DRIVER;
+  CUtensorMap map;
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(p.cols) * 2};
+  const cuuint32_t box[2] = {kTile, kTile};
+  const cuuint32_t estr[2] = {1, 1};
+  if (fn(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(p.x), dims, strides, box, estr,
+         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return MXB200_ERR_DRIVER;
+  static std::atomic<int> configured_for{-1};
+  int device = 0;
+  cudaGetDevice(&device);
+  if (configured_for.load() != device) {
+    if (cudaFuncSetAttribute(mxb200_quantize_bf16_stream, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(kStreamSmemBytes)) != cudaSuccess)
+      return MXB200_ERR_LAUNCH;
+    configured_for.store(device);
+  }
+  static std::atomic<uint32_t> next_slot{0};
+  const StreamParams sp{p, static_cast<int>(tiles), static_cast<int>(next_slot.fetch_add(1) % kStreamSchedSlots)};
+  const unsigned grid = static_cast<unsigned>(std::min<int64_t>(tiles, kStreamCtasPerSm * static_cast<int64_t>(sms)));
+  mxb200_quantize_bf16_stream<<<grid, kThreads, kStreamSmemBytes, stream>>>(map, sp);
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return launch_status();
+}
+
 int quantize(const void* x, const void* h, bool x_bf16, int64_t rows, int64_t cols, mxb200_mx_out out,
              mxb200_mx_out out_t, int pro, int scale_rule, void* stream, const SoftcapGrad* ce = nullptr,
              int64_t ld = 0) {
@@ -484,6 +716,9 @@ int quantize(const void* x, const void* h, bool x_bf16, int64_t rows, int64_t co
     return launch<true, kNone>(p, tiles, s);
   switch (pro) {
     case kNone:
+      // more tiles than the one-shot kernel holds at once (4 CTAs per SM): stream them through persistent CTAs
+      if (tiles > 4 * static_cast<int64_t>(dev.sms))
+        return launch_stream(p, rows, cols, tiles, dev.sms, s);
       return launch<false, kNone>(p, tiles, s);
     case kReluSquare:
       return launch<false, kReluSquare>(p, tiles, s);
@@ -569,6 +804,22 @@ int quantize_batch(const mxb200_quantize_job* jobs, int n_jobs, bool x_bf16, int
 }  // namespace
 
 }  // namespace mxb200
+
+namespace mxb200 {
+uint32_t take_quantize_watchdog_word() {
+  uint32_t w = 0;
+  if (cudaMemcpyFromSymbol(&w, g_quantize_watchdog_word, sizeof(w)) != cudaSuccess)
+    return 0;
+  if (w != 0) {
+    const uint32_t zero = 0;
+    cudaMemcpyToSymbol(g_quantize_watchdog_word, &zero, sizeof(zero));
+    static const uint32_t zeros[2 * kStreamSchedSlots] = {};
+    cudaMemcpyToSymbol(g_quantize_sched, zeros, sizeof(zeros));
+  }
+  return w;
+}
+}  // namespace mxb200
+
 
 extern "C" int mxb200_quantize_mx_batch(const mxb200_quantize_job* jobs, int n_jobs, int x_bf16, int scale_rule,
                                         void* stream) {

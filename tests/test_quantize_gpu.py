@@ -146,6 +146,82 @@ def test_full_size_roundtrip_property():
     assert (deqt.t() - x.float()).norm() / x.float().norm() < 0.04
 
 
+# ---- the streaming form: plain bf16 tensors of more than 4 tiles per SM (592 on a B200) go through persistent CTAs
+
+STREAM_SHAPE = (2048, 5120)  # 640 tiles
+
+
+def _stream_input(seed=11):
+    x = quantizer_input(*STREAM_SHAPE, seed=seed)
+    x[3, 5] = float("nan")
+    x[130, 64:96] = float("nan")  # a block of only NaN
+    x[5, 100] = float("inf")
+    x[700, 130] = float("-inf")
+    x[7, :] = 0
+    x[8, 0:32] = 3e38
+    x[9, 32:64] = 1e-45
+    x[10, 64:96] = -0.0
+    return x.to(torch.bfloat16)
+
+
+@pytest.mark.parametrize("rule", [nc.SCALE_REFERENCE, nc.SCALE_OCP_FLOOR])
+def test_streaming_form_matches_oracle(rule):
+    """Same bytes as the oracle on a tensor large enough for the persistent kernel, edge values included."""
+    x = _stream_input()
+    q = nc.quantize_mx(x.cuda(), scale_rule=rule)
+    assert_quantized_equal(q, oracle_quantize(x, rule=rule), f"streaming form, rule {rule}")
+    assert nc.capi.device_status() == 0
+
+
+def test_streaming_form_rows_only_and_cols_only():
+    x = _stream_input(seed=12)
+    want = oracle_quantize(x)
+    q = nc.quantize_mx(x.cuda(), True, False)
+    assert_quantized_equal(q, {k: want[k] for k in ("data", "scale")}, "streaming form, rows only")
+    q = nc.quantize_mx(x.cuda(), False, True)
+    assert_quantized_equal(q, {k: want[k] for k in ("data_t", "scale_t")}, "streaming form, cols only")
+
+
+def test_streaming_form_equals_one_shot_kernel_at_full_size():
+    """Config 2's activation (1536 tiles, persistent kernel) against the same tensor quantized in slices of 512 rows
+    (48 tiles each, one CTA per tile): same bytes and scales in both layouts."""
+    g = torch.Generator(device="cuda").manual_seed(4)
+    R, C, S = 16384, 1536, 512
+    x = (torch.randn(R, C, generator=g, device="cuda") * torch.logspace(-3, 3, C, device="cuda")).to(torch.bfloat16)
+    q = nc.quantize_mx(x)
+    sc = q.inv_scale.view(torch.uint8).view(R // 128, C // 128, 512)
+    sct = q.inv_scale_t.view(torch.uint8).view(C // 128, R // 128, 512)
+    for i in range(R // S):
+        part = nc.quantize_mx(x[i * S:(i + 1) * S])
+        assert torch.equal(part.data.view(torch.uint8), q.data[i * S:(i + 1) * S].view(torch.uint8))
+        assert torch.equal(part.data_t.view(torch.uint8), q.data_t[:, i * S:(i + 1) * S].view(torch.uint8))
+        assert torch.equal(part.inv_scale.view(torch.uint8).view(S // 128, C // 128, 512), sc[i * S // 128:(i + 1) * S // 128])
+        assert torch.equal(part.inv_scale_t.view(torch.uint8).view(C // 128, S // 128, 512),
+                           sct[:, i * S // 128:(i + 1) * S // 128])
+
+
+def test_streaming_form_overlapping_launches_and_slot_reuse():
+    """Launches of the persistent kernel that overlap on two streams each draw tiles from their own counter, and a
+    counter is handed back zeroed: 600 launches (the library keeps 256 counters) all give the first launch's bytes."""
+    x = _stream_input(seed=13).cuda()
+    want = nc.quantize_mx(x)
+    torch.cuda.synchronize()
+    streams = [torch.cuda.Stream(), torch.cuda.Stream()]
+    outs = [[nc.empty_mx(*STREAM_SHAPE, x.device) for _ in range(2)] for _ in streams]
+    for k in range(300):
+        for s, mine in zip(streams, outs):
+            with torch.cuda.stream(s):
+                out, out_t = nc.mx_outs(mine[k & 1])
+                nc.quantize_mx_into(x, False, out, out_t)
+    torch.cuda.synchronize()
+    for mine in outs:
+        for q in mine:
+            for a, b in ((q.data, want.data), (q.inv_scale, want.inv_scale), (q.data_t, want.data_t),
+                         (q.inv_scale_t, want.inv_scale_t)):
+                assert torch.equal(a.view(torch.uint8), b.view(torch.uint8))
+    assert nc.capi.device_status() == 0
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_batch_equals_separate_calls(dtype):
     """mxb200_quantize_mx_batch: 40 tensors of mixed shapes (more than one launch holds), some into sub-views of a
