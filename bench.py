@@ -385,7 +385,7 @@ def run_gpu_arm(args):
                          "peak_source": peak_source, "peak_2x_bf16_sustained": fp8_2x, "peak_cublaslt_mxfp8_8192": fp8_lt,
                          "frac_of_fp8_spec_4500": achieved / FP8_SPEC_TFLOPS,
                          "launches": n_gemm, "avg_launch_us": gemm_ms * 1e3 / max(n_gemm, 1)},
-            "quantizer": {"bound": "hbm", "kernel": "mxb200_quantize_bf16 / mxb200_quantize_batch_f32", "achieved": cfg.quantized_bytes_per_step() * args.steps / (quant_ms * 1e-3) / 1e9,
+            "quantizer": {"bound": "hbm", "kernel": "mxb200_quantize_bf16_stream / mxb200_quantize_batch_f32", "achieved": cfg.quantized_bytes_per_step() * args.steps / (quant_ms * 1e-3) / 1e9,
                           "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": cfg.quantized_bytes_per_step() * args.steps / (quant_ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
                           "launches": n_quant, "ms_per_step": quant_ms / args.steps, "gb_per_step": cfg.quantized_bytes_per_step() / 1e9},
             "ms_per_step_split": {"gemm": gemm_ms / args.steps, "quantize": quant_ms / args.steps,
