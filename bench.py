@@ -21,6 +21,7 @@ fp32 matmul, oracle/torch_reference.py) on a bounded sample, on the host cores.
 from __future__ import annotations
 
 import argparse
+import gc
 import json
 import os
 import statistics
@@ -213,8 +214,17 @@ def run_gpu_arm(args):
 
     # ---- device-resident timing: the timed region carries no per-launch events (an event record per launch boundary
     # costs a few percent of a step)
+    # The timed steps replay CUDA graphs of the step (one per phase of the input rotation; captured after eager steps
+    # have configured the kernels): the same launches, and at N > 1 the same collectives on their side stream, without
+    # the host between them. Warm-up runs both forms.
+    use_graph = not args.no_graph
     for i in range(args.warmup):
-        step.run_step(i)
+        step.run_step(i, eager=True)
+    if use_graph:
+        barrier()
+        step.capture()
+        for i in range(args.warmup):
+            step.run_step(i)
     barrier()
     sampler = ClockSampler(local_rank)
     if rank == 0:
@@ -227,7 +237,8 @@ def run_gpu_arm(args):
         step.run_step(args.warmup + i)
     t_end.record()
     barrier()
-    launches = nc.capi.launch_count() - launches0
+    # a replayed graph launches the kernels counted while it was captured
+    launches = step.launches_per_step * args.steps if use_graph else nc.capi.launch_count() - launches0
     ms_total = t_begin.elapsed_time(t_end)
 
     # ---- the same steps once more with CUDA events around every GEMM and quantizer launch: the per-kernel durations
@@ -236,7 +247,7 @@ def run_gpu_arm(args):
     i_begin, i_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     i_begin.record()
     for i in range(args.steps):
-        step.run_step(args.warmup + args.steps + i)
+        step.run_step(args.warmup + args.steps + i, eager=True)
     i_end.record()
     barrier()
     collect[0] = False
@@ -284,17 +295,26 @@ def run_gpu_arm(args):
             del qa, qb, out
         except Exception as e:
             extra["fp8_cublaslt_error"] = repr(e)[:200]
-        step.set_wgrad_fp32_accumulate(True)
         k = [0]
 
         def acc_step():
             step.run_step(k[0])
             k[0] += 1
-        extra["fp32_accumulate_ms"] = timed_ms(acc_step, min(args.steps, 5))
+
+        def other_form_ms():  # the step in another form, launched as the timed steps are
+            step.run_step(0, eager=True)
+            if use_graph:
+                step.capture()
+            return timed_ms(acc_step, min(args.steps, 5))
+        step.set_wgrad_fp32_accumulate(True)
+        extra["fp32_accumulate_ms"] = other_form_ms()
         step.set_wgrad_fp32_accumulate(False)
         step.cfg.real_producers = True
-        extra["real_producers_ms"] = timed_ms(acc_step, min(args.steps, 5))
+        extra["real_producers_ms"] = other_form_ms()
         step.cfg.real_producers = False
+        step.release()
+        if use_graph:
+            step.capture()
         watchdog = watchdog or nc.capi.device_status()
 
     # ---- end to end: one full set of every per-step input of the path (the activations and residual each Linear
@@ -369,7 +389,9 @@ def run_gpu_arm(args):
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "fp8_e4m3 (ue8m0 block scales, fp32 accumulate)", "data": "synthetic",
             "config": {"workload": WORKLOAD, "tflop_per_rank_step": flops / 1e12, "global_tokens": cfg.tokens * world,
-                       "parallelism": f"dp{world}", "l2": "operands and outputs of every launch exceed or rotate past the 126 MB L2 (9+ GB touched per step)",
+                       "parallelism": f"dp{world}",
+                       "launch": "CUDA graph replay of the step" if use_graph else "every kernel launched from the host",
+                       "l2": "operands and outputs of every launch exceed or rotate past the 126 MB L2 (9+ GB touched per step)",
                        "collective": (f"bf16 reduce-scatter (avg) of whole matrices per rank in the reference's stack segments over NCCL "
                                       f"({'NCCL default CTAs' if nccl_max_ctas <= 0 else 'max ' + str(nccl_max_ctas) + ' CTAs'}), overlapped with backward") if world > 1 else "none (1 rank)"},
             "per_gpu_tflops": value / world,
@@ -421,10 +443,15 @@ def run_gpu_arm(args):
         if watchdog != 0:
             line["invalid"] = f"a bounded device wait ran out (status word {watchdog:#x}): results are not trusted"
         print(json.dumps(line), flush=True)
-        if watchdog != 0:
-            raise SystemExit(3)
+    # the graphs hold the collectives they captured: they go before the communicator does
+    step.release()
+    gc.collect()
+    torch.cuda.synchronize()
     if world > 1:
+        dist.barrier()
         dist.destroy_process_group()
+    if watchdog != 0:
+        raise SystemExit(3)
 
 
 def main():
@@ -433,6 +460,8 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", type=str, default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-graph", action="store_true",
+                    help="launch every kernel of the timed steps from the host instead of replaying CUDA graphs of the step")
     ap.add_argument("--no-comparators", action="store_true",
                     help="skip the cuBLASLt / fp32-accumulate / CPU legs (a short run of the step alone, for a profiler)")
     args = ap.parse_args()

@@ -295,10 +295,13 @@ class DpStep:
         self.gemm_only = False
         self.comm_stream = torch.cuda.Stream(device=device) if (device.type == "cuda" and world > 1) else None
         self._pending: list = []
+        self._graphs = None            # CUDA graphs of the step, one per phase of the input rotation (capture())
+        self.launches_per_step = None  # library kernels in one captured step
 
     def set_wgrad_fp32_accumulate(self, on: bool):
         """Switches the weight-gradient form (StepConfig.wgrad_fp32_accumulate); the fp32 .grad buffers (4 bytes per
         parameter) are allocated on first use."""
+        self._graphs = None  # a captured step has the other form baked in
         self.cfg.wgrad_fp32_accumulate = on
         if on and self.grads is None:
             cfg, device = self.cfg, self.device
@@ -541,7 +544,41 @@ class DpStep:
             torch.cuda.current_stream().wait_stream(self.comm_stream)
 
     # ------------------------------------------------------------------ the step
-    def run_step(self, step: int = 0):
+    def capture(self) -> None:
+        """Records the step as CUDA graphs, one per phase of the input rotation (step k reads input set (k + layer) %
+        n_sets), after which run_step replays them: the step's 555 launches, and with more than one rank its
+        collectives with their side stream and events, are then issued by the device's front end without the host
+        between them, which takes the gaps between launches (1 to 1.5 ms of a 41 ms step) out. Call it after an eager
+        step (first launches configure kernels and allocate the split-K workspace) and again after changing the
+        step's form; `release()` or a form change drops the graphs."""
+        n_sets = len(self.x_attn)
+        self._graphs = None
+        stream = torch.cuda.Stream(device=self.device)
+        graphs, pool = [], None
+        for phase in range(n_sets):
+            g = torch.cuda.CUDAGraph()
+            before = nc.capi.launch_count()
+            # thread_local: NCCL's watchdog thread and the clock sampler make CUDA calls of their own meanwhile
+            with torch.cuda.graph(g, pool=pool, stream=stream, capture_error_mode="thread_local"):
+                self._run_step_eager(phase)
+            self.launches_per_step = nc.capi.launch_count() - before
+            pool = g.pool()
+            graphs.append(g)
+        self._graphs = graphs
+
+    def release(self) -> None:
+        self._graphs = None
+
+    def run_step(self, step: int = 0, eager: bool = False):
+        """One step. Replays the captured graph of this step's phase when `capture()` has been called, unless `eager`
+        (per-launch hooks only see eager launches) or the GEMM-only comparator form is on."""
+        if self._graphs is not None and not eager and not self.gemm_only:
+            with nvtx_range("step (graph replay)"):
+                self._graphs[step % len(self._graphs)].replay()
+            return
+        self._run_step_eager(step)
+
+    def _run_step_eager(self, step: int = 0):
         cfg = self.cfg
         n_sets = len(self.x_attn)
         with nvtx_range("quantize_weights"):

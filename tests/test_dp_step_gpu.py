@@ -71,3 +71,32 @@ def test_step_with_real_producers():
     assert torch.isfinite(st["loss"]).all() and float(st["loss"].mean()) > 0
     assert torch.isfinite(s.bucket.buffer.float()).all()
     assert nc.capi.device_status() == 0
+
+
+def test_graph_replay_equals_eager_launches():
+    """capture() records the step once per phase of the input rotation; a replay writes the bytes the eager launches
+    write, for both phases and for the fp32-accumulate form after a re-capture."""
+    dev = torch.device("cuda", 0)
+    s = DpStep(small(), dev)
+    eager = []
+    for k in range(2):
+        s.run_step(k, eager=True)
+        eager.append((s.bucket.buffer.clone(), s.qkv.clone(), s.dx.clone(), s.gq_4c.data_t.clone().view(torch.uint8)))
+    s.capture()
+    assert s.launches_per_step > 0
+    for k in (0, 1, 2, 3):
+        s.bucket.buffer.zero_()
+        s.run_step(k)
+        want = eager[k % 2]
+        got = (s.bucket.buffer, s.qkv, s.dx, s.gq_4c.data_t.view(torch.uint8))
+        for g, w in zip(got, want):
+            assert torch.equal(g, w)
+    s.set_wgrad_fp32_accumulate(True)  # drops the graphs: the next step is launched eagerly
+    s.run_step(0)
+    s.capture()
+    base = [g.clone() for g in s.grads[1]]
+    s.run_step(0)
+    for g, b in zip(s.grads[1], base):
+        assert torch.equal(g, 2 * b)
+    assert torch.equal(s.bucket.buffer, 2 * eager[0][0])  # the cast of gradients accumulated over two micro-steps
+    assert nc.capi.device_status() == 0
