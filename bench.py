@@ -10,8 +10,10 @@ written as bf16 into the reference's stacked send buffers and, for N > 1, reduce
 (71.74 TFLOP of GEMM per rank and step). Inputs are seeded synthetic tensors of the BASELINE shapes and
 distributions; there is no dataset or checkpoint on this path.
 
-value: GEMM TFLOP/s of the whole job (all ranks), from device time of the timed steps, inputs resident in HBM.
-The steps are then run a second time with CUDA events around every launch, which gives the per-kernel durations.
+value: GEMM TFLOP/s of the whole job (all ranks), from device time of the timed steps, inputs resident in HBM. The
+timed steps replay CUDA graphs of the step, captured after eager warm-up steps (--no-graph launches every kernel from
+the host instead). The steps are then run a second time, launched from the host, with CUDA events around every launch,
+which gives the per-kernel durations.
 e2e: the same with one full set of every per-step input (activations, residual, incoming gradients, lm_head
 activations and logit gradients: everything but the weights) copied from pinned host memory inside the timed region
 (on a copy stream, one step ahead, as a loader would) and a slice of the result read back every step. roofline: the GEMM kernel alone, bracketed by CUDA events on its stream.
