@@ -224,7 +224,20 @@ def run_gpu_arm(args):
         step.run_step(i, eager=True)
     if use_graph:
         barrier()
-        step.capture()
+        try:
+            step.capture()
+            captured = 1
+        except Exception as e:  # a driver or library that cannot capture the step: fall back to host launches
+            print(f"bench.py: graph capture failed on rank {rank} ({e!r:.300}); launching from the host", file=sys.stderr)
+            step.release()
+            captured = 0
+        if world > 1:  # all ranks run the same form
+            agreed = torch.tensor([captured], device=device)
+            dist.all_reduce(agreed, op=dist.ReduceOp.MIN)
+            captured = int(agreed.item())
+        if not captured:
+            step.release()
+            use_graph = False
         for i in range(args.warmup):
             step.run_step(i)
     barrier()
