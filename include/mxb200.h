@@ -224,7 +224,7 @@ MXB200_API int mxb200_device_status(uint32_t* word);
 MXB200_API int mxb200_selftest_bounded_wait(uint64_t limit_ns, void* stream);
 
 /* Tuning knobs for measurement, process-wide. tile_n: 128 or 256 = the one-CTA kernel with 128 x tile_n tiles;
- * 640 / 384 / 512 = the CTA-pair kernel (256 x 128 / 256 x 192 / 256 x 256 tile over two SMs); 0 = choose per shape. max_ctas: CTAs of the persistent
+ * 384 / 512 = the CTA-pair kernel (256 x 192 / 256 x 256 tile over two SMs); 0 = choose per shape. max_ctas: CTAs of the persistent
  * grid (0 = one per SM). Not part of the reference interface. */
 MXB200_API int mxb200_set_gemm_config(int tile_n, int max_ctas);
 

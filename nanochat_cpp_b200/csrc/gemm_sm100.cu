@@ -861,8 +861,7 @@ __device__ __forceinline__ bool sched_read(Barriers* bars, uint32_t seq, bool ar
 // TN = 256: the widest tile (least L2 traffic per flop); its two accumulator buffers overlap by 32 columns, so
 // the next tile's first MMA waits until the previous tile's epilogue has read those columns: a bubble of about
 // 1500 cycles per tile, negligible for long K. TN = 192: two disjoint buffers, no bubble, for shapes with a
-// short main loop. TN = 128: a third more operand bytes per flop again, for the few shapes whose wider tilings leave
-// a third of the CTA pairs without a tile (the (C, C) weight gradient: 72 tiles instead of 48 for 74 pairs). Scale tiles of B are loaded as the two 128-row tiles covering the tile's columns; the tile's
+// short main loop. Scale tiles of B are loaded as the two 128-row tiles covering the tile's columns; the tile's
 // first column is ((n * TN) % 128) / 32 TMEM columns into the first of them. That offset must be even: a scale
 // address at an odd column (a tile starting 32 or 96 rows into a scale tile, as a 224-wide tiling would) is a
 // misaligned-address fault, so tile widths are multiples of 64.
@@ -877,8 +876,7 @@ constexpr int kEpiFusedBytes = 6144;       // ... with a fused quantizer: output
 
 template <int TN, int kFuse = kFuseNone>
 struct PairConfig {
-  static_assert(TN == 128 || TN == 192 || TN == 256, "tile width");
-  static_assert(TN != 128 || kFuse == kFuseNone, "the fused-quantize epilogues come 192 and 256 wide");
+  static_assert(TN == 192 || TN == 256, "tile width");
   static constexpr int kEpiBytes = kFuse == kFuseNone ? kEpiStageBytes : kEpiFusedBytes;
   static constexpr int kParts = kFuse == kFuseNone ? 2 : 3;
   static constexpr int kEpiWarps = 4 * kParts;
@@ -891,7 +889,7 @@ struct PairConfig {
   static constexpr uint32_t kBBytes = kBRows * kBK;
   static constexpr uint32_t kSfBytes = kScaleTileBytes * (1 + kSfbTiles);  // A: own 128 rows; B: all its tiles
   static constexpr uint32_t kTxPerCta = kABytes + kBBytes + kSfBytes;
-  static constexpr int kStages = (TN == 128 ? 8 : TN == 192 ? 7 : 6) - (kFuse == kFuseNone ? 0 : 2);
+  static constexpr int kStages = (TN == 192 ? 7 : 6) - (kFuse == kFuseNone ? 0 : 2);
   static constexpr bool kOverlap = TN == 256;
   static constexpr uint32_t kAcc0 = 0, kAcc1 = kOverlap ? 224 : TN;
   static constexpr uint32_t kSfaCol = kOverlap ? 480 : 2 * TN, kSfbCol = kSfaCol + 4;
@@ -1368,7 +1366,6 @@ __device__ __forceinline__ void pair_kernel_body(const CUtensorMap* map_a, const
 
 MXB200_GEMM_KERNEL(mxb200_gemm_128x128, 128)
 MXB200_GEMM_KERNEL(mxb200_gemm_128x256, 256)
-MXB200_GEMM_PAIR_KERNEL(mxb200_gemm_pair_256x128, 128, mxb200::kFuseNone)
 MXB200_GEMM_PAIR_KERNEL(mxb200_gemm_pair_256x192, 192, mxb200::kFuseNone)
 MXB200_GEMM_PAIR_KERNEL(mxb200_gemm_pair_256x256, 256, mxb200::kFuseNone)
 MXB200_GEMM_PAIR_KERNEL(mxb200_gemm_pair_256x192_relu_square, 192, mxb200::kFuseReluSquare)
@@ -1395,7 +1392,7 @@ constexpr GemmPairKernel pair_kernel() {
   else if constexpr (kFuse == kFuseReluSquareBwd)
     return TN == 256 ? mxb200_gemm_pair_256x256_relu_square_bwd : mxb200_gemm_pair_256x192_relu_square_bwd;
   else
-    return TN == 256 ? mxb200_gemm_pair_256x256 : TN == 192 ? mxb200_gemm_pair_256x192 : mxb200_gemm_pair_256x128;
+    return TN == 256 ? mxb200_gemm_pair_256x256 : mxb200_gemm_pair_256x192;
 }
 
 // ------------------------------------------------------------------------------------------------ host side
@@ -1452,8 +1449,8 @@ int make_scale_map(CUtensorMap* map, const void* base, int64_t rows, int64_t k, 
   return r == CUDA_SUCCESS ? MXB200_OK : MXB200_ERR_DRIVER;
 }
 
-// How a shape is tiled: one-CTA kernel with 128 x 128 or 128 x 256 tiles, or the CTA-pair kernel with 256 x 128,
-// 256 x 192 or 256 x 256.
+// How a shape is tiled: one-CTA kernel with 128 x 128 or 128 x 256 tiles, or the CTA-pair kernel with 256 x 192
+// or 256 x 256.
 struct TilePlan {
   bool pair;
   int tile_m, tile_n;
@@ -1469,16 +1466,12 @@ TilePlan plan_tiles(int64_t M, int64_t N, int64_t K, int sms, bool need_pair = f
   if (need_pair && (forced == 128 || forced == 256))
     forced = 0;  // the fused-quantize epilogues exist in the CTA-pair kernel only
   TilePlan t{};
-  if (need_pair && forced == 640)
-    forced = 0;  // ... and not 128 wide
-  if (forced == 640 || forced == 512 || forced == 384 || need_pair || (forced == 0 && M >= 256 && N >= 256)) {
+  if (forced == 512 || forced == 384 || need_pair || (forced == 0 && M >= 256 && N >= 256)) {
     t.pair = true, t.tile_m = 256, t.slots = std::max(sms / 2, 1);
     if (forced == 512) {
       t.tile_n = 256;
     } else if (forced == 384) {
       t.tile_n = 192;
-    } else if (forced == 640) {
-      t.tile_n = 128;
     } else {
       // Estimated cycles: waves x (main loop + the hand-over between tiles). The main loop runs at the slower of
       // MMA execution (2 TN cycles per K step of 128) and what an SM can ingest (about 64 bytes per cycle); 256
@@ -1487,9 +1480,7 @@ TilePlan plan_tiles(int64_t M, int64_t N, int64_t K, int sms, bool need_pair = f
       // more than it gains, see mxb200_gemm_splits).
       const int64_t k_iters = K / 128;
       double best = 0.0;
-      for (int tn : {256, 192, 128}) {
-        if (tn == 128 && need_pair)
-          break;
+      for (int tn : {256, 192}) {
         const int64_t tiles = ((M + 255) / 256) * ((N + tn - 1) / tn);
         const int64_t units = tiles, iters = k_iters;
         // Pairs draw their tiles from a counter, so with many short tiles per pair the launch ends within a fraction
@@ -1562,10 +1553,6 @@ int launch_pair(const PairMaps& m, const GemmParams& p, int pairs, cudaStream_t 
 
 template <int kFuse>
 int launch_pair_width(int tile_n, const PairMaps& m, const GemmParams& p, int pairs, cudaStream_t stream) {
-  if constexpr (kFuse == kFuseNone) {
-    if (tile_n == 128)
-      return launch_pair<128, kFuse>(m, p, pairs, stream);
-  }
   return tile_n == 256 ? launch_pair<256, kFuse>(m, p, pairs, stream) : launch_pair<192, kFuse>(m, p, pairs, stream);
 }
 
@@ -1769,7 +1756,7 @@ extern "C" int mxb200_gemm_splitk(const void* a, const void* a_scale, const void
 }
 
 extern "C" int mxb200_set_gemm_config(int tile_n, int max_ctas) {
-  if ((tile_n != 0 && tile_n != 128 && tile_n != 256 && tile_n != 384 && tile_n != 512 && tile_n != 640) || max_ctas < 0)
+  if ((tile_n != 0 && tile_n != 128 && tile_n != 256 && tile_n != 384 && tile_n != 512) || max_ctas < 0)
     return MXB200_ERR_ARGUMENT;
   mxb200::g_tile_n.store(tile_n);
   mxb200::g_max_ctas.store(max_ctas);

@@ -45,7 +45,7 @@ def _default_config():
 
 
 @pytest.mark.parametrize("M,N,K", SHAPES)
-@pytest.mark.parametrize("tile_n", [128, 256, 384, 512, 640])
+@pytest.mark.parametrize("tile_n", [128, 256, 384, 512])
 def test_bf16_and_f32_match_oracle(M, N, K, tile_n):
     nc.capi.lib.mxb200_set_gemm_config(tile_n, 0)
     qa, qb = quantized(M, N, K)
@@ -87,7 +87,7 @@ def test_f32_accumulate_with_device_alpha(M, N, K):
     assert rel(acc, 2 * once) < 1e-6
 
 
-@pytest.mark.parametrize("tile_n", [128, 256, 384, 512, 640])
+@pytest.mark.parametrize("tile_n", [128, 256, 384, 512])
 def test_fused_residual_is_bit_exact_with_separate_add(tile_n):
     """bf16(float(bf16(acc)) + resid): the reference's separate x + r (residual_norm_kernel.cu:96-104)."""
     nc.capi.lib.mxb200_set_gemm_config(tile_n, 0)
@@ -107,7 +107,7 @@ def test_fused_residual_is_bit_exact_with_separate_add(tile_n):
 
 
 @pytest.mark.parametrize("M,N", [(256, 384), (256, 640), (384, 384), (640, 896), (128, 1024)])
-@pytest.mark.parametrize("tile_n", [256, 384, 512, 640])
+@pytest.mark.parametrize("tile_n", [256, 384, 512])
 def test_partial_last_tiles(M, N, tile_n):
     """N % 256 == 128 (and, for the CTA-pair kernel, M % 256 == 128): the last tile is half empty."""
     nc.capi.lib.mxb200_set_gemm_config(tile_n, 0)
@@ -124,7 +124,7 @@ def test_partial_last_tiles(M, N, tile_n):
 
 
 @pytest.mark.parametrize("splits", [2, 3, 4])
-@pytest.mark.parametrize("tile_n", [128, 256, 384, 512, 640])
+@pytest.mark.parametrize("tile_n", [128, 256, 384, 512])
 def test_split_k_matches_single_pass_and_is_deterministic(splits, tile_n):
     """The weight-gradient shape class: long K, few tiles. Slices are summed in fixed order."""
     nc.capi.lib.mxb200_set_gemm_config(tile_n, 0)
