@@ -463,9 +463,11 @@ __device__ __forceinline__ void quantize_stream(const CUtensorMap* map_x, const 
 
   // Thread 0 posts this CTA's i-th tile and starts its load into buffer i % stages. A number past the last tile is the
   // stop sign: posted once (a bare arrival completes the phase), after which nothing more is drawn or posted.
-  // The first `stages` tiles of a CTA are fixed (blockIdx.x + i * gridDim.x), so no load at the start waits for an
-  // atomic; the launch's counter hands out the tiles from stages * gridDim.x on, and each draw is issued a whole tile
-  // before its number is needed.
+  // A CTA's first tile is its own number, so its first load does not wait for an atomic; every later tile comes from
+  // the launch's counter, which starts at gridDim.x, and each draw is issued a whole tile before its number is needed
+  // (the second tile's at the very start, behind the first load). Only one tile is fixed because a CTA may start late:
+  // when another kernel (a collective on a side stream) holds SMs, the CTAs that do not fit wait until others have run
+  // out of tiles, and whatever is fixed to them is then worked on after everything else.
   bool drawing = true;
   auto post = [&](int i, int tile) {
     const int s = i % kStreamStages;
@@ -480,16 +482,18 @@ __device__ __forceinline__ void quantize_stream(const CUtensorMap* map_x, const 
     tma_load_2d_hint(1u, smem_raw + s * kStreamTileBytes, map_x, &bars->full[s], (tile % p.tiles_c) * kTile,
                      (tile / p.tiles_c) * kTile, l2_policy_evict_first());
   };
-  if (t == 0)
-    for (int i = 0; i < kStreamStages && drawing; ++i)
-      post(i, static_cast<int>(blockIdx.x + i * gridDim.x));
+  if (t == 0) {
+    post(0, static_cast<int>(blockIdx.x));
+    for (int i = 1; i < kStreamStages && drawing; ++i)
+      post(i, static_cast<int>(gridDim.x + atomicAdd(&sched[0], 1u)));
+  }
 
   int i = 0;
   for (;; ++i) {
     const int s = i % kStreamStages;
     int drawn = 0;  // thread 0: the tile of iteration i + stages, asked for now and posted after this tile
     if (t == 0 && drawing)
-      drawn = static_cast<int>(kStreamStages * gridDim.x + atomicAdd(&sched[0], 1u));
+      drawn = static_cast<int>(gridDim.x + atomicAdd(&sched[0], 1u));
     const bool landed = stream_wait(&bars->full[s], static_cast<uint32_t>(i / kStreamStages) & 1u, bars,
                                     kStreamWaitLimitNs, static_cast<uint32_t>(i));
     const int tile = landed ? *reinterpret_cast<volatile int*>(&bars->tile_of[s]) : -1;
