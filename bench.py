@@ -220,7 +220,7 @@ def run_gpu_arm(args):
     # have configured the kernels): the same launches, and at N > 1 the same collectives on their side stream, without
     # the host between them. Warm-up runs both forms.
     use_graph = not args.no_graph
-    for i in range(args.warmup):
+    for i in range(max(args.warmup, 1) if use_graph else args.warmup):  # a capture needs one eager step before it
         step.run_step(i, eager=True)
     if use_graph:
         barrier()
